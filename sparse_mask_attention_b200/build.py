@@ -17,7 +17,7 @@ LIB_NAME = "libsma_b200.so"
 LIB_PATH = os.path.join(PKG_DIR, LIB_NAME)
 
 SOURCES = ["sma_capi.cu"]
-HEADERS = ["sma_common.cuh", "sma_pack.cuh", "sma_attention.cuh", os.path.join("..", "..", "include", "sma.h")]
+HEADERS = ["sma_common.cuh", "sma_pack.cuh", "sma_plan.cuh", "sma_attention.cuh", os.path.join("..", "..", "include", "sma.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -74,9 +74,39 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
+// Tensor maps are pure functions of (base address, shape, element type, box), and encoding one costs the host
+// about a microsecond; a step of a training or serving loop passes the same few tensors again and again.  Each
+// host thread therefore keeps the maps it encoded last in a small direct-mapped table.
+struct TensorMapKey {
+    const void* base;
+    int32_t bh;
+    int32_t n;
+    int32_t kind;  // box rows for q/k/v/out maps (fp16), + 1000 for bf16, -1 for the packed-mask map
+    bool operator==(const TensorMapKey& o) const { return base == o.base && bh == o.bh && n == o.n && kind == o.kind; }
+};
+struct TensorMapSlot {
+    TensorMapKey key = {nullptr, 0, 0, 0};
+    CUtensorMap map;
+};
+constexpr int kTensorMapSlots = 64;
+thread_local TensorMapSlot tls_tensor_maps[kTensorMapSlots];
+
+TensorMapSlot& tensor_map_slot(const TensorMapKey& key) {
+    const uintptr_t a = reinterpret_cast<uintptr_t>(key.base);
+    const size_t h = (a >> 8) * 0x9E3779B97F4A7C15ull + static_cast<size_t>(key.kind) * 0x632BE5ABull +
+                     static_cast<size_t>(key.n) * 31u + static_cast<size_t>(key.bh);
+    return tls_tensor_maps[(h >> 20) % kTensorMapSlots];
+}
+
 // Tensor map over a [BH, N, 64] row-major 16-bit tensor; one box = box_rows x 64 elements of one
 // (batch, head), written to shared memory with the 128-byte swizzle.  Rows past N read as zeros.
 int make_qkv_tensor_map(CUtensorMap* map, const void* base, int BH, int N, int box_rows, bool bf16) {
+    const TensorMapKey key = {base, BH, N, box_rows + (bf16 ? 1000 : 0)};
+    TensorMapSlot& slot = tensor_map_slot(key);
+    if (slot.key == key) {
+        *map = slot.map;
+        return SMA_OK;
+    }
     EncodeTiledFn encode = encode_tiled_fn();
     if (!encode) return SMA_ERR_CUDA;
     const cuuint64_t dims[3] = {64, static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(BH)};
@@ -91,6 +121,43 @@ int make_qkv_tensor_map(CUtensorMap* map, const void* base, int BH, int N, int b
         tls_cuda_error = static_cast<int>(cudaErrorInvalidValue);
         return SMA_ERR_CUDA;
     }
+    slot.key = key;
+    slot.map = *map;
+    return SMA_OK;
+}
+
+// Whether the packed mask [BH, N, nw] can be described by a tensor map: 16-byte aligned base and row pitch.
+bool mask_has_tensor_map(const uint32_t* base, int N) {
+    const int nw = (N + 31) / 32;
+    return (reinterpret_cast<uintptr_t>(base) & 15u) == 0 && (nw % 4) == 0;
+}
+
+// Tensor map over the packed mask [BH, N, nw] (32-bit words); one box = the 16 words x 128 rows a work item
+// needs for one chunk of 512 keys, dense in shared memory (64 bytes per row).  Words past nw and rows past N
+// read as zeros.
+int make_mask_tensor_map(CUtensorMap* map, const uint32_t* base, int BH, int N) {
+    const TensorMapKey key = {base, BH, N, -1};
+    TensorMapSlot& slot = tensor_map_slot(key);
+    if (slot.key == key) {
+        *map = slot.map;
+        return SMA_OK;
+    }
+    EncodeTiledFn encode = encode_tiled_fn();
+    if (!encode) return SMA_ERR_CUDA;
+    const cuuint64_t nw = static_cast<cuuint64_t>((N + 31) / 32);
+    const cuuint64_t dims[3] = {nw, static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(BH)};
+    const cuuint64_t strides[2] = {nw * 4, static_cast<cuuint64_t>(N) * nw * 4};
+    const cuuint32_t box[3] = {sma::kChunkWords, sma::kBlockM, 1};
+    const cuuint32_t elem_strides[3] = {1, 1, 1};
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<uint32_t*>(base), dims, strides, box,
+                              elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        tls_cuda_error = static_cast<int>(cudaErrorInvalidValue);
+        return SMA_ERR_CUDA;
+    }
+    slot.key = key;
+    slot.map = *map;
     return SMA_OK;
 }
 
@@ -113,11 +180,11 @@ cudaError_t launch_overlapped(void (*kernel)(KArgs...), unsigned blocks, unsigne
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...);
 }
 
-template <bool kBf16, bool kSplitP, int kStreams, bool kPlanned>
+template <bool kBf16, bool kSplitP, bool kPlanned>
 int launch_attention(DeviceInfo* dev, int slot, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                     const CUtensorMap& to, const sma::AttnArgs& args, cudaStream_t stream) {
-    auto kernel = sma::attn_fwd_kernel<kBf16, kSplitP, kStreams, kPlanned>;
-    constexpr size_t smem = sma::attn_smem_bytes<kStreams>();
+                     const CUtensorMap& to, const CUtensorMap& tm, const sma::AttnArgs& args, cudaStream_t stream) {
+    auto kernel = sma::attn_fwd_kernel<kBf16, kSplitP, kPlanned>;
+    constexpr size_t smem = sma::attn_smem_bytes();
     // One CTA per SM: the kernel allocates all 512 tensor-memory columns, and more than half of the
     // SM's shared memory keeps a second CTA from becoming resident next to it.
     static_assert(smem > 116 * 1024 && smem <= 227 * 1024, "shared memory must pin occupancy to one CTA per SM");
@@ -132,7 +199,7 @@ int launch_attention(DeviceInfo* dev, int slot, const CUtensorMap& tq, const CUt
     }
     const long long items = static_cast<long long>(args.BH) * args.num_q_tiles;
     const unsigned blocks = static_cast<unsigned>(items < dev->sm_count ? items : dev->sm_count);
-    return cuda_ok(launch_overlapped(kernel, blocks, sma::attn_threads<kStreams>(), smem, stream, tq, tk, tv, to, args))
+    return cuda_ok(launch_overlapped(kernel, blocks, sma::kAttnThreads, smem, stream, tq, tk, tv, to, tm, args))
                ? SMA_OK
                : SMA_ERR_CUDA;
 }
@@ -237,11 +304,17 @@ static int attention_forward(const sma_attention_params* p, uint32_t* plan, void
     if (int st = current_device_info(&dev)) return st;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
 
-    CUtensorMap tq, tk, tv, to;
+    CUtensorMap tq, tk, tv, to, tm;
     if (int st = make_qkv_tensor_map(&tq, p->q, static_cast<int>(BH), p->N, sma::kBlockM, bf16)) return st;
-    if (int st = make_qkv_tensor_map(&to, p->out, static_cast<int>(BH), p->N, sma::kBlockM, bf16)) return st;
+    if (int st = make_qkv_tensor_map(&to, p->out, static_cast<int>(BH), p->N, sma::kStageRowsOut, bf16)) return st;
     if (int st = make_qkv_tensor_map(&tk, p->k, static_cast<int>(BH), p->N, sma::kBlockN, bf16)) return st;
     if (int st = make_qkv_tensor_map(&tv, p->v, static_cast<int>(BH), p->N, sma::kBlockN, bf16)) return st;
+    const bool mask_tma = mask_has_tensor_map(p->mask_packed, p->N);
+    if (mask_tma) {
+        if (int st = make_mask_tensor_map(&tm, p->mask_packed, static_cast<int>(BH), p->N)) return st;
+    } else {
+        tm = tq;  // never used by the kernel: the loader warps copy the mask words with plain loads
+    }
 
     sma::AttnArgs args;
     args.mask_packed = p->mask_packed;
@@ -254,19 +327,20 @@ static int attention_forward(const sma_attention_params* p, uint32_t* plan, void
     args.scale_log2e = std::fabs(p->scale) * 1.4426950408889634f;
     args.negate_q = p->scale < 0.f ? 1u : 0u;
     args.save_lse = p->save_lse ? 1 : 0;
+    args.mask_tma = mask_tma ? 1 : 0;
 
     if (plan) {
         const unsigned items = static_cast<unsigned>(BH * num_q_tiles);
         sma::build_tile_lists_kernel<<<items, sma::kPlanRows, 0, stream>>>(p->mask_packed, plan, static_cast<int>(BH),
                                                                           p->N, num_q_tiles, args.plan_stride);
         if (!cuda_ok(cudaGetLastError())) return SMA_ERR_CUDA;
-        if (!bf16) return launch_attention<false, false, 2, true>(dev, 4, tq, tk, tv, to, args, stream);
-        if (split_p) return launch_attention<true, true, 2, true>(dev, 5, tq, tk, tv, to, args, stream);
-        return launch_attention<true, false, 2, true>(dev, 6, tq, tk, tv, to, args, stream);
+        if (!bf16) return launch_attention<false, false, true>(dev, 4, tq, tk, tv, to, tm, args, stream);
+        if (split_p) return launch_attention<true, true, true>(dev, 5, tq, tk, tv, to, tm, args, stream);
+        return launch_attention<true, false, true>(dev, 6, tq, tk, tv, to, tm, args, stream);
     }
-    if (!bf16) return launch_attention<false, false, 2, false>(dev, 0, tq, tk, tv, to, args, stream);
-    if (split_p) return launch_attention<true, true, 2, false>(dev, 1, tq, tk, tv, to, args, stream);
-    return launch_attention<true, false, 2, false>(dev, 2, tq, tk, tv, to, args, stream);
+    if (!bf16) return launch_attention<false, false, false>(dev, 0, tq, tk, tv, to, tm, args, stream);
+    if (split_p) return launch_attention<true, true, false>(dev, 1, tq, tk, tv, to, tm, args, stream);
+    return launch_attention<true, false, false>(dev, 2, tq, tk, tv, to, tm, args, stream);
 }
 
 // Bytes of workspace for B x H x N, or 0 for a shape the attention entry points reject.
@@ -288,13 +362,6 @@ int sma_attention_fwd_planned(const sma_attention_params* p, void* workspace, si
     if (need != 0 && workspace_bytes < need) return SMA_ERR_WORKSPACE_TOO_SMALL;
     return attention_forward(p, static_cast<uint32_t*>(workspace), stream_v);  // need == 0: the shape checks report it
 }
-
-#ifdef SMA_TRACE
-// Development hook: installs a device buffer of 2 * 4000 long longs for the timeline trace.
-int sma_debug_set_trace(long long* device_buffer) {
-    return cuda_ok(cudaMemcpyToSymbol(sma::g_trace_buf, &device_buffer, sizeof(device_buffer))) ? SMA_OK : SMA_ERR_CUDA;
-}
-#endif
 
 // ---- the entry point that allocates nothing -----------------------------------------------------------------
 // Built-in workspace of sma_attention_fwd_static_workspace.  It lives in the library's device image: every GPU
@@ -326,6 +393,10 @@ int sma_attention_fwd_static_workspace(const sma_attention_params* p, void* stre
     if (!p) return SMA_ERR_NULL_POINTER;
     const size_t need = attention_workspace_bytes(p->B, p->H, p->N);
     if (need > SMA_STATIC_WORKSPACE_BYTES) return SMA_ERR_STATIC_WORKSPACE_EXCEEDED;
+    // the device is looked at before the array's address: on a GPU for which the library holds no code the
+    // caller should hear SMA_ERR_WRONG_ARCH, like from the other entry points, not a failed symbol look-up
+    DeviceInfo* dev = nullptr;
+    if (int st = current_device_info(&dev)) return st;
     uint32_t* workspace = nullptr;
     if (int st = static_workspace_of_current_device(&workspace)) return st;
     // Nothing in the workspace has to start at zero: the tile-list kernel writes every word the attention kernel

@@ -1,7 +1,7 @@
 // Device-side building blocks for sm_100a: mbarrier, TMA (cp.async.bulk.tensor), tensor memory
 // (tcgen05.alloc/ld/st) and tcgen05.mma, written as thin inline-PTX wrappers.
 //
-// Every wait in this file is bounded: after SMA_SPIN_LIMIT unsuccessful polls it gives up, records
+// Every wait in this file is bounded: after kWaitLimitCycles of the SM clock it gives up, records
 // SMA_ERR_DEVICE_TIMEOUT in the device status word and returns false, so a kernel can release its
 // tensor memory and return instead of hanging the GPU.
 #pragma once
@@ -18,31 +18,7 @@ namespace sma {
 // a single translation unit, so this definition is the only one.
 __device__ int g_device_status = 0;
 
-// Optional timeline trace for kernel development (compiled in only with -DSMA_TRACE): selected threads
-// append (tag, SM clock) pairs to a global buffer installed with sma_debug_set_trace().
-#ifdef SMA_TRACE
-__device__ long long* g_trace_buf = nullptr;
-struct TraceCursor {
-    long long* p;
-    int n;
-};
-#define SMA_TRACE_DECL(cur, enabled, offset) \
-    sma::TraceCursor cur{(enabled) && sma::g_trace_buf ? sma::g_trace_buf + (offset) : nullptr, 0}
-#define SMA_TRACE_POINT(cur, tag)                         \
-    do {                                                  \
-        if ((cur).p && (cur).n < 2000) {                  \
-            (cur).p[2 * (cur).n] = (tag);                 \
-            (cur).p[2 * (cur).n + 1] = clock64();         \
-            ++(cur).n;                                    \
-        }                                                 \
-    } while (0)
-#else
-#define SMA_TRACE_DECL(cur, enabled, offset) ((void)0)
-#define SMA_TRACE_POINT(cur, tag) ((void)0)
-#endif
-
 constexpr int kDeviceTimeout = -10;          // == SMA_ERR_DEVICE_TIMEOUT
-constexpr uint32_t kSpinLimit = 1u << 24;    // polls of mbarrier.try_wait before giving up
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -72,15 +48,24 @@ __device__ __forceinline__ void mbar_init_fence() {
 __device__ __forceinline__ void mbar_arrive_expect_tx_a(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
-    mbar_arrive_expect_tx_a(smem_u32(bar), bytes);
-}
-
 __device__ __forceinline__ void mbar_arrive_a(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) { mbar_arrive_a(smem_u32(bar)); }
-
+// Non-blocking test: has the phase with the given parity completed?  (mbarrier.try_wait, below, may block for a
+// system-dependent time, a microsecond or two, before it answers "no".)
+__device__ __forceinline__ bool mbar_test_wait_a(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ bool mbar_try_wait_a(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
@@ -94,10 +79,6 @@ __device__ __forceinline__ bool mbar_try_wait_a(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    return mbar_try_wait_a(smem_u32(bar), parity);
-}
-
 // Suspending poll: the thread sleeps in the barrier unit until the phase completes or the hint (in
 // nanoseconds) runs out, instead of spinning through the instruction scheduler it shares with working warps.
 __device__ __forceinline__ bool mbar_try_wait_suspend_a(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
@@ -114,19 +95,11 @@ __device__ __forceinline__ bool mbar_try_wait_suspend_a(uint32_t bar, uint32_t p
     return ok != 0;
 }
 
-// Bounded wait for the phase with the given parity to complete.  Returns false on timeout.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-    }
-    atomicExch(&g_device_status, kDeviceTimeout);
-    return false;
-}
-
-// Same, for CTAs whose threads wait on one another: the first wait that runs out raises *abort_flag
-// (a word in shared memory), and every other waiter of the CTA gives up at its next poll instead of
-// running out its own limit.  The limit is kWaitLimitCycles of the SM clock (a second or two), not a
-// poll count: a poll may return at once or sleep for the whole hint.
+// Bounded wait for the phase with the given parity, for CTAs whose threads wait on one another: the first
+// wait that runs out raises *abort_flag (a word in shared memory) and the device status word, and every
+// other waiter of the CTA gives up at its next poll instead of running out its own limit.  The limit is
+// kWaitLimitCycles of the SM clock (a second or two), not a poll count: a poll may return at once or sleep
+// for the whole hint.
 constexpr long long kWaitLimitCycles = 1ll << 32;
 constexpr uint32_t kSuspendHintNs = 20000;
 __device__ __forceinline__ bool mbar_wait_a(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
@@ -141,8 +114,59 @@ __device__ __forceinline__ bool mbar_wait_a(uint32_t bar, uint32_t parity, volat
     atomicExch(&g_device_status, kDeviceTimeout);
     return false;
 }
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
-    return mbar_wait_a(smem_u32(bar), parity, abort_flag);
+
+// ------------------------------------------------------------------------------------------------
+// Shared-memory accesses by 32-bit address, and global loads that stay coherent
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float lds_f32(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint2 lds_v2(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts_u16(uint32_t addr, uint32_t v) {
+    asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"(static_cast<uint16_t>(v)) : "memory");
+}
+__device__ __forceinline__ void sts_u32(uint32_t addr, uint32_t v) {
+    asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void sts_f32(uint32_t addr, float v) {
+    asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void sts_v4(uint32_t addr, uint4 v) {
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+// Plain (coherent) global loads.  Kernels launched with programmatic stream serialisation are resident while
+// their predecessor still writes, so data a predecessor produces must not go through the non-coherent path
+// (ld.global.nc / __ldg), whose lines are only valid for data that is read-only during the whole kernel.
+__device__ __forceinline__ uint32_t ldg_u32(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint32_t ldg_u16(const uint16_t* p) {
+    uint16_t v;
+    asm volatile("ld.global.u16 %0, [%1];" : "=h"(v) : "l"(p) : "memory");
+    return v;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -160,11 +184,6 @@ __device__ __forceinline__ void tma_load_3d_a(uint32_t smem_dst, const CUtensorM
         "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
         : "memory");
 }
-__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* tmap, uint64_t* bar, int32_t c0,
-                                            int32_t c1, int32_t c2) {
-    tma_load_3d_a(smem_u32(smem_dst), tmap, smem_u32(bar), c0, c1, c2);
-}
-
 // TMA store shared -> global of one tile (rows outside the tensor are clipped), tracked by bulk groups.
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap* tmap, const void* smem_src, int32_t c0, int32_t c1,
                                              int32_t c2) {
@@ -233,6 +252,17 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "memory");
 }
 
+// 16-column variant of the load above.
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+
 // Same load, results delivered as fp32 values into dst[0..31] (dst indexes a register array).
 __device__ __forceinline__ void tmem_ld32_f32(uint32_t taddr, float* dst) {
     asm volatile(
@@ -291,42 +321,6 @@ __host__ __device__ constexpr uint32_t make_idesc(uint32_t a_fmt, uint32_t b_fmt
 // eight 128-byte rows are 1024 bytes apart (stride byte offset); the leading byte offset is unused
 // when the swizzled extent covers the whole row.  The same encoding serves K-major operands
 // (rows = M or N index, contraction along the row) and MN-major operands (rows = contraction index).
-__device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);  // start address
-    d |= static_cast<uint64_t>(1) << 16;                      // leading byte offset (ignored)
-    d |= static_cast<uint64_t>(1024 >> 4) << 32;              // stride byte offset
-    d |= static_cast<uint64_t>(1) << 46;                      // descriptor version for sm_100
-    d |= static_cast<uint64_t>(2) << 61;                      // SWIZZLE_128B
-    return d;
-}
-
-// D[tmem] (+)= A[smem] * B[smem]
-__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                       uint32_t accumulate) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
-        "}\n" ::"r"(d_tmem),
-        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-// D[tmem] (+)= A[tmem] * B[smem]
-__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                       uint32_t accumulate) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
-        "}\n" ::"r"(d_tmem),
-        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
 // The same two products with the 64-bit shared-memory descriptors given as (low word, common high word):
 // the high word of every 128-byte-swizzle descriptor is the same constant, and stepping through a tile
 // only changes the low word, so the issuing thread does 32-bit arithmetic only.
@@ -366,8 +360,6 @@ constexpr uint32_t kSmemDescSw128Hi = (1024u >> 4) | (1u << 14) | (2u << 29);
 __device__ __forceinline__ void mma_commit_a(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void mma_commit(uint64_t* bar) { mma_commit_a(smem_u32(bar)); }
-
 // ------------------------------------------------------------------------------------------------
 // Small math helpers
 // ------------------------------------------------------------------------------------------------

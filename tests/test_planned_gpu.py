@@ -1,10 +1,10 @@
 """sma_attention_fwd_planned (tile lists computed ahead into a caller's workspace) against sma_attention_fwd
 (tile lists found inside the attention kernel): same inputs, bitwise the same outputs; workspace checks."""
-import ctypes
-
+import numpy as np
 import pytest
 import torch
 
+import gpu_util as gu
 from sparse_mask_attention_b200 import _capi, sparse_attn_cuda, workloads
 
 pytestmark = pytest.mark.gpu
@@ -47,6 +47,73 @@ def test_planned_equals_unplanned_bitwise(N, kind, dtype):
         _capi.device_status()
         outs.append((out, lse))
     assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    # and both agree with the fp32 oracle on these inputs, not only with each other
+    ref, ref_lse = gu.oracle_for(q, k, v, mask)
+    gu.assert_close(gu.to_np32(outs[1][0]), ref, "planned N=%d %s" % (N, kind))
+    gu.assert_lse_close(outs[1][1].cpu().numpy(), ref_lse, "planned N=%d %s" % (N, kind))
+
+
+@pytest.mark.parametrize("planned", [False, True])
+def test_many_row_blocks_that_keep_nothing(planned):
+    # 960 work items (128-row blocks) on 296 streams, three quarters of them without a single kept key, scattered:
+    # every stream meets runs of empty items between non-empty ones, which is where a tile-list slot could be
+    # recycled while a consumer still has to read it
+    B, H, N = 10, 12, 1024
+    cfg = workloads.Config("empty_blocks", B, H, N, torch.float16, "iid", 0.3, seed=77)
+    q, k, v, mask = workloads.make_inputs(cfg)
+    g = torch.Generator().manual_seed(78)
+    dead = torch.rand(B, H, N // 128, generator=g) < 0.75
+    mask &= ~dead.repeat_interleave(128, dim=-1)[..., None]
+    qd, kd, vd, md = (t.cuda() for t in (q, k, v, mask))
+    packed = sparse_attn_cuda.pack_mask(md)
+    out = torch.full_like(qd, 3.0)
+    lse = torch.full((B, H, N), 7.0, dtype=torch.float32, device="cuda")
+    p = _params(qd, kd, vd, packed, out, lse)
+    if planned:
+        nbytes = _capi.attention_workspace_bytes(B, H, N)
+        ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+        _capi.attention_fwd_planned(p, ws.data_ptr(), nbytes, None)
+    else:
+        _capi.attention_fwd(p, None)
+    torch.cuda.synchronize()
+    _capi.device_status()
+    ref, ref_lse = gu.oracle_for(q, k, v, mask)
+    gu.assert_close(gu.to_np32(out), ref, "empty row blocks")
+    gu.assert_lse_close(lse.cpu().numpy(), ref_lse, "empty row blocks")
+    empty = ~mask.numpy().any(axis=-1)
+    assert empty.mean() > 0.7 and not gu.to_np32(out)[empty].any()
+
+
+def test_pack_then_forward_into_reused_buffers_without_synchronising():
+    # three different masks packed into ONE packed buffer and attended into ONE output buffer, all queued on the
+    # stream before anything is waited for: each forward must see its own pack's words although the attention
+    # kernel becomes resident while the pack kernel before it is still writing them
+    B, H, N = 4, 6, 512
+    cases = []
+    for seed, kind, keep in ((31, "iid", 0.25), (32, "block", 0.3), (33, "causal_iid", 0.5)):
+        cfg = workloads.Config("reuse", B, H, N, torch.float16, kind, keep, seed=seed)
+        cases.append(tuple(t.cuda() for t in workloads.make_inputs(cfg)))
+    want = []
+    for q, k, v, mask in cases:
+        out = torch.empty_like(q)
+        sparse_attn_cuda.forward(q, k, v, sparse_attn_cuda.pack_mask(mask), out, None, 0.125, False)
+        torch.cuda.synchronize()
+        want.append(out)
+    packed = torch.empty(B, H, N, N // 32, dtype=torch.int32, device="cuda")
+    out = torch.empty_like(cases[0][0])
+    got = []
+    torch.cuda.synchronize()
+    for q, k, v, mask in cases:
+        _capi.pack_mask(mask.data_ptr(), packed.data_ptr(), B, H, N, None)
+        lse = torch.empty(B, H, N, dtype=torch.float32, device="cuda")
+        p = _params(q, k, v, packed, out, lse)
+        p.save_lse = 0
+        _capi.attention_fwd(p, None)
+        got.append(out.clone())  # a copy kernel on the same stream, still nothing synchronised
+    torch.cuda.synchronize()
+    _capi.device_status()
+    for w, g_ in zip(want, got):
+        assert torch.equal(w, g_)
 
 
 def test_workspace_size_and_errors():

@@ -9,14 +9,19 @@ run every other test.  It needs nothing from the other tests and passes in a fre
 import pytest
 import torch
 
+import gpu_util as gu
 from sparse_mask_attention_b200 import _capi, sparse_attn_cuda, workloads
 
 pytestmark = pytest.mark.gpu
 
 
-def _case(B, H, N, kind, keep, dtype, seed):
+def _inputs(B, H, N, kind, keep, dtype, seed):
     cfg = workloads.Config("no_alloc", B, H, N, dtype, kind, keep, seed=seed)
-    q, k, v, mask = (t.cuda() for t in workloads.make_inputs(cfg))
+    return workloads.make_inputs(cfg)
+
+
+def _case(B, H, N, kind, keep, dtype, seed):
+    q, k, v, mask = (t.cuda() for t in _inputs(B, H, N, kind, keep, dtype, seed))
     return q, k, v, sparse_attn_cuda.pack_mask(mask)
 
 
@@ -53,6 +58,41 @@ def test_two_calls_in_a_row_match_the_allocating_entry_point():
     assert torch.equal(again[0][0], want[1][0]) and torch.equal(again[1][0], want[0][0])
     # the outputs above are torch's; the entry point itself took nothing from the device
     assert free_after >= free_before - (2 << 20)
+    # and the results are right, not merely equal to one another: the fp32 oracle on the same inputs
+    for (B, H, N, kind, keep, dtype, seed), (o_got, l_got) in zip(
+            [(1, 2, 2048, "block", 0.1, torch.float16, 21), (2, 3, 320, "iid", 0.3, torch.bfloat16, 22)], got):
+        q, k, v, mask = _inputs(B, H, N, kind, keep, dtype, seed)
+        ref, ref_lse = gu.oracle_for(q, k, v, mask)
+        gu.assert_close(gu.to_np32(o_got), ref, "static workspace N=%d" % N)
+        gu.assert_lse_close(l_got.cpu().numpy(), ref_lse, "static workspace N=%d" % N)
+
+
+def test_calls_queued_without_synchronising_each_see_their_own_tile_lists():
+    # Four calls of different shapes and masks queued on one stream, nothing waited for in between.  They all
+    # use the same built-in array, and each attention kernel becomes resident while the tile-list kernel before
+    # it is still running: it must read that kernel's lists, never a stale copy of the previous call's.
+    specs = [(2, 4, 512, "block", 0.2, torch.float16, 41), (1, 3, 1024, "causal_iid", 0.5, torch.bfloat16, 42),
+             (3, 2, 384, "iid", 0.1, torch.float16, 43), (2, 4, 512, "block", 0.6, torch.float16, 44)]
+    cases = [_case(*s) for s in specs]
+    want = [_call(_capi.attention_fwd, *c) for c in cases]
+    outs = []
+    torch.cuda.synchronize()
+    for q, k, v, packed in cases:
+        B, H, N, D = q.shape
+        out = torch.full_like(q, 5.0)
+        lse = torch.full((B, H, N), 9.0, dtype=torch.float32, device=q.device)
+        p = _capi.AttentionParams()
+        p.q, p.k, p.v, p.mask_packed = q.data_ptr(), k.data_ptr(), v.data_ptr(), packed.data_ptr()
+        p.out, p.lse = out.data_ptr(), lse.data_ptr()
+        p.B, p.H, p.N, p.D, p.scale = B, H, N, D, D ** -0.5
+        p.dtype = _capi.SMA_DTYPE_F16 if q.dtype == torch.float16 else _capi.SMA_DTYPE_BF16
+        p.save_lse, p.variant = 1, _capi.SMA_VARIANT_DEFAULT
+        _capi.attention_fwd_static_workspace(p, None)
+        outs.append((out, lse))
+    torch.cuda.synchronize()
+    _capi.device_status()
+    for (o_want, l_want), (o_got, l_got) in zip(want, outs):
+        assert torch.equal(o_got, o_want) and torch.equal(l_got, l_want)
 
 
 def test_shapes_beyond_the_built_in_workspace_are_refused():
