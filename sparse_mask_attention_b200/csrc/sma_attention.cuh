@@ -6,7 +6,7 @@
 // (csrc/sparse_attention.cu:82-412) and sparse_attention_fwd_kernel<...,bf16> (:418-543): rows with no
 // kept column give zeros, masked columns contribute exactly nothing.
 //
-// Structure: one persistent CTA of 512 threads per SM runs two independent "streams".  A stream owns one work
+// Structure: one persistent CTA of 384 threads per SM runs two independent "streams".  A stream owns one work
 // item at a time — 128 consecutive query rows of one (batch, head) — walks its keys in chunks of 512 (eight
 // 64-key tiles, sixteen packed-mask words per row) and visits only the tiles that hold at least one kept bit
 // for those rows.  Warp roles:
@@ -19,19 +19,19 @@
 //     without draining, and issues every tcgen05.mma of the stream:
 //         S[128x64]  = Q K^T   (operands in shared memory)
 //         O[128x64] += P V     (P from tensor memory, V MN-major from shared memory)
-//     S runs one tile ahead of the softmax threads (two S/P buffers); Q and O are double-buffered, so the
-//     first products of the next item run while the previous item is still being finished.
+//     S runs two tiles ahead of the softmax threads (three S/P buffers) and Q is double-buffered, so the
+//     first S products of the next item run while the previous item is still being finished; the next item's
+//     first P V waits until the softmax warps have copied the previous item's O out of tensor memory.
 //   * softmax warps (4 per stream): thread r owns query row r (tensor-memory lane r).  Per tile it reads
 //     its S row with tcgen05.ld, applies its two mask words from the strip, updates the running max / sum
 //     and writes P (16-bit) with tcgen05.st over the columns its S row came from.  At the end of an item it
-//     leaves 1/sum in shared memory for the epilogue warps and goes straight on to the next item.
-//   * epilogue warps (4, shared by both streams): warp w owns rows 32w..32w+31 (its tensor-memory lane
-//     quadrant) of whichever stream finishes an item: it reads O, normalises, rounds, stages the rows in
-//     shared memory and stores them with one TMA store.
+//     goes straight on to the first tile of the next item (whose S is ready) and finishes the previous item
+//     behind that tile, when its last P V has long completed: each warp reads its 32 rows of O, normalises,
+//     rounds, stages them in shared memory and stores them with one TMA store.
 // Hand-offs are mbarriers (TMA transaction counts, tcgen05.commit, thread arrivals); every wait is bounded.
 // Orderings that need no barrier of their own, because one thread issues all products of a stream and the
 // tensor core runs them in issue order:
-//   * S(j) may overwrite buffer j%2 once P V(j-2) has been issued: that product read the buffer's previous P.
+//   * S(j) may overwrite buffer j%3 once P V(j-3) has been issued: that product read the buffer's previous P.
 //   * P(j) may overwrite S(j) in place: the softmax threads read S(j) before they write P(j).
 #pragma once
 
@@ -51,12 +51,12 @@ constexpr int kSlots = 2;          // chunks (mask strip + descriptor) in flight
 constexpr int kChunkTiles = 8;     // key tiles per chunk
 constexpr int kChunkWords = 2 * kChunkTiles;       // packed-mask words per row and chunk
 constexpr int kChunkKeys = kBlockN * kChunkTiles;  // 512
-constexpr int kAttnThreads = 512;
+constexpr int kAttnThreads = 384;
 
-// Tensor-memory layout of one stream (256 columns): two S/P buffers (64 columns each; P takes the first
-// 32 of them, or all 64 as hi|lo halves for the bf16 split), then two O accumulators (64 each).
+// Tensor-memory layout of one stream (256 columns): three S/P buffers (64 columns each; P takes the first
+// 32 of them, or all 64 as hi|lo halves for the bf16 split), then the O accumulator (64).
 constexpr int kColsPerStream = 256;
-constexpr int kSBuffers = 2;
+constexpr int kSBuffers = 3;
 constexpr int kColS = 0;
 constexpr int kColO = 64 * kSBuffers;
 
@@ -94,27 +94,26 @@ static_assert(sizeof(ChunkDesc) == 32, "descriptor addressing below assumes 32 b
 struct StreamCtrl {
     alignas(8) uint64_t bar_q[2];          // TMA: Q tile of item r landed in buffer r % 2
     uint64_t bar_q_free[2];                // tcgen05.commit: every S of item r is complete
-    uint64_t bar_kv[kStages];              // TMA: K and V tile landed
+    uint64_t bar_k[kStages];               // TMA: K tile landed
+    uint64_t bar_v[kStages];               // TMA: V tile landed
     uint64_t bar_pv_done[kStages];         // tcgen05.commit: P V complete (the K/V stage is free again)
     uint64_t bar_s_full[kSBuffers];        // tcgen05.commit: S tile complete
     uint64_t bar_p_full[kSBuffers];        // 128 arrivals: P written over the S buffer (and O rescaled)
     uint64_t bar_list_full[kSlots];        // 1 arrival: chunk descriptor published
     uint64_t bar_strip_full[kSlots];       // TMA (or 1 arrival): the chunk's mask strip is in shared memory
     uint64_t bar_slot_free[kSlots];        // 129 arrivals: softmax threads and MMA warp left the chunk
-    uint64_t bar_stat_full[2];             // 128 arrivals: row sums of item r published
-    uint64_t bar_o_full[2];                // tcgen05.commit: every P V of item r is complete
-    uint64_t bar_o_free[2];                // 4 arrivals: the epilogue warps have read O and the row sums
+    uint64_t bar_o_full;                   // tcgen05.commit: every P V of item r is complete (one phase per item)
+    uint64_t bar_o_free;                   // 4 arrivals: the softmax warps have read O of item r
     ChunkDesc desc[kSlots];
-    int32_t stat_item[2];                  // work item the row sums belong to (< 0: the stream has ended)
-    float stat_inv_l[2][kBlockM];          // 1 / row sum (0 for a row that keeps nothing)
 };
 
 struct AttnSmem {
     StreamTiles tiles[kNumStreams];
-    alignas(1024) uint8_t staging[4][kStageRowsOut * 128];  // one per epilogue warp
+    alignas(1024) uint8_t staging[kNumStreams][4][kStageRowsOut * 128];  // one per softmax warp
     StreamCtrl ctrl[kNumStreams];
     uint32_t tmem_base;
     uint32_t abort_flag;  // raised by the first bounded wait that runs out
+    uint32_t next_item;   // how many of the CTA's work items its two streams have taken
 };
 
 constexpr size_t attn_smem_bytes() { return sizeof(AttnSmem) + 1024; }  // + slack to align the base to 1024
@@ -130,6 +129,52 @@ __device__ __noinline__ void rescale_o_row(uint32_t addr, float alpha) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
         tmem_st32(addr + half * 32, o);
+    }
+}
+
+// One warp's share of the end of a work item: its 32 rows of the O accumulator (tensor-memory lanes of the
+// warp's quadrant, 64 fp32 columns at o_addr) times the row's 1/sum, rounded to 16 bit, staged in the warp's
+// shared-memory tile (128-byte swizzle, as the tensor map of `out` expects) and stored with one TMA store of
+// 32 rows.  inv_l == 0 marks a row that keeps nothing: it is written as zeros whatever the accumulator holds.
+// Arrives on bar_o_free once O is in registers.  Kept out of line: it runs once per work item, and the tile
+// loop around its call site is sensitive to the size of its body.
+template <bool kBf16>
+__device__ __noinline__ void finish_rows(uint32_t o_addr, float inv_l, uint32_t a_stage, uint32_t a_bar_o_free,
+                                         const CUtensorMap* tmap_o, int row0, int bh, bool store) {
+    const int lane = threadIdx.x & 31;
+    // the previous store of this warp must have finished reading the staging tile
+    if (lane == 0) tma_store_wait_read();
+    __syncwarp();
+    // row `lane` of the warp occupies 128 bytes; its 16-byte chunk j sits at chunk position j ^ (lane & 7)
+    const uint32_t a_row = a_stage + lane * 128;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        uint32_t o[32];
+        tmem_ld32(o_addr + half * 32, o);
+        tmem_wait_ld();
+        if (half == 1) {
+            // O is in registers (or already staged): the stream may overwrite it
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_a(a_bar_o_free);
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            uint32_t pk[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float x = __uint_as_float(o[8 * q + 2 * j]) * inv_l;
+                const float y = __uint_as_float(o[8 * q + 2 * j + 1]) * inv_l;
+                pk[j] = inv_l == 0.f ? 0u : (kBf16 ? pack_bf16x2(x, y) : pack_f16x2(x, y));
+            }
+            sts_v4(a_row + (((4 * half + q) ^ (lane & 7)) << 4), make_uint4(pk[0], pk[1], pk[2], pk[3]));
+        }
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0 && store) {
+        tma_store_3d(tmap_o, reinterpret_cast<const void*>(__cvta_shared_to_generic(a_stage)), 0, row0, bh);
+        tma_store_commit();
     }
 }
 
@@ -160,17 +205,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 const __grid_constant__ CUtensorMap tmap_m, const AttnArgs args) {
     static_assert(kBf16 || !kSplitP, "the hi+lo split exists for bf16 only");
     static_assert(kNumStreams * kColsPerStream <= kTmemCols, "tensor memory over-committed");
-    static_assert(kSlots == 2 && kSBuffers == 2, "slot and buffer indices below are ordinal & 1");
-    // register budgets: 512 threads start at 128 registers each; 256 * 200 + 256 * 56 = 512 * 128
-    constexpr int kRegsSoftmax = 200;
-    constexpr int kRegsOther = 56;
+    static_assert(kSlots == 2, "slot indices below are ordinal & 1");
+    // register budgets: 384 threads start at 168 registers each; 256 * 216 + 128 * 72 = 384 * 168
+    constexpr int kRegsSoftmax = 216;
+    constexpr int kRegsOther = 72;
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     AttnSmem& sm = *reinterpret_cast<AttnSmem*>(smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u));
 
-    // Warpgroup 0 holds the MMA warps (warps 0, 1) and the loader warps (2, 3) of the two streams, warpgroups
-    // 1 and 2 are the softmax warps of stream 0 and 1, warpgroup 3 the epilogue warps.  warp % 4 decides the
+    // Warpgroup 0 holds the P V warps (warps 0, 1) and the loader warps (2, 3) of the two streams, warpgroups
+    // 1 and 2 are the softmax warps of stream 0 and 1.  warp % 4 decides the
     // tensor-memory lane quadrant a warp may touch.  The index is broadcast from lane 0 so that the compiler
     // knows it (and every address derived from it) to be the same in all lanes of a warp and keeps such values
     // in uniform registers: tcgen05.mma, the TMA instructions and the barrier instructions take their operands
@@ -184,7 +229,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const int nw = (N + 31) >> 5;                             // packed words per mask row
     const int num_chunks = (N + kChunkKeys - 1) / kChunkKeys;
     const int total_items = BH * args.num_q_tiles;
-    const int item_stride = kNumStreams * static_cast<int>(gridDim.x);
 
     // ---- set-up: barriers (one thread per stream), tensor memory (one warp) --------------------------
     if ((wg == 1 || wg == 2) && (threadIdx.x & 127) == 0) {
@@ -192,20 +236,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         for (int s = 0; s < 2; ++s) {
             mbar_init(&ct.bar_q[s], 1);
             mbar_init(&ct.bar_q_free[s], 1);
-            mbar_init(&ct.bar_s_full[s], 1);
-            mbar_init(&ct.bar_p_full[s], 128);
             mbar_init(&ct.bar_list_full[s], 1);
             mbar_init(&ct.bar_strip_full[s], 1);
             mbar_init(&ct.bar_slot_free[s], 129);
-            mbar_init(&ct.bar_stat_full[s], 128);
-            mbar_init(&ct.bar_o_full[s], 1);
-            mbar_init(&ct.bar_o_free[s], 4);
+        }
+        mbar_init(&ct.bar_o_full, 1);
+        mbar_init(&ct.bar_o_free, 4);
+        for (int s = 0; s < kSBuffers; ++s) {
+            mbar_init(&ct.bar_s_full[s], 1);
+            mbar_init(&ct.bar_p_full[s], 128);
         }
         for (int s = 0; s < kStages; ++s) {
-            mbar_init(&ct.bar_kv[s], 1);
+            mbar_init(&ct.bar_k[s], 1);
+            mbar_init(&ct.bar_v[s], 1);
             mbar_init(&ct.bar_pv_done[s], 1);
         }
-        if (wg == 1) sm.abort_flag = 0u;
+        if (wg == 1) {
+            sm.abort_flag = 0u;
+            sm.next_item = 0u;
+        }
         mbar_init_fence();
     }
     __syncwarp();
@@ -220,96 +269,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     grid_launch_dependents();
     grid_dependency_wait();
 
-    // Work items are dealt round-robin: item j belongs to CTA j % grid; the CTA's items go to its streams
-    // in turn (stream s takes items blockIdx + s*grid, then every 2*grid further).  Item j is
+    // Work items are dealt round-robin to the CTAs: item j belongs to CTA j % grid.  Inside the CTA the two
+    // streams take its items one at a time as they become free (a counter in shared memory), so that a stream
+    // which the warp schedulers favour, or whose items hold fewer tiles, does more of them.  Item j is
     // (row block, batch*head) with the later row blocks first: for causal-like masks they hold most work.
     auto item_bh = [&](int item) { return item % BH; };
     auto item_row0 = [&](int item) { return (args.num_q_tiles - 1 - item / BH) * kBlockM; };
     bool ok = true;  // false once a bounded wait has run out; the same in all lanes of a warp
     volatile uint32_t* const abort_flag = &sm.abort_flag;
-    // Bounded wait on an mbarrier phase.  After a failure nothing is waited for any more, and the warp's lanes
-    // agree on the outcome (the .sync.aligned instructions that follow need a converged warp).
+    // Bounded wait on an mbarrier phase.  After a failure nothing is waited for any more.  The lanes of a warp
+    // test the barrier with one instruction and so take the fast path together; on the polling path they agree
+    // on the outcome before they go on (the .sync.aligned instructions that follow need a converged warp).
     auto wait = [&](uint32_t bar, uint32_t parity) {
-        if (ok) ok = __all_sync(0xFFFFFFFFu, mbar_wait_a(bar, parity, abort_flag));
+        if (ok && !mbar_try_wait_a(bar, parity)) ok = __all_sync(0xFFFFFFFFu, mbar_wait_poll(bar, parity, abort_flag));
     };
 
-    if (wg == 3) {
-        // =========================================== epilogue warps ==========================================
-        setmaxnreg_dec<kRegsOther>();
-        const uint32_t a_stage = smem_u32(sm.staging[wq]);
-        const uint32_t tmem_q = sm.tmem_base + (static_cast<uint32_t>(wq * 32) << 16);
-        uint32_t e[kNumStreams] = {0u, 0u};       // items finished per stream
-        bool done[kNumStreams] = {false, false};
-        long long t_idle = clock64();
-        bool staged = false;  // a TMA store of this warp may still be reading the staging tile
-        while (ok && !(done[0] && done[1])) {
-            bool progressed = false;
-#pragma unroll
-            for (int s = 0; s < kNumStreams; ++s) {
-                if (done[s]) continue;
-                const uint32_t ct_a = smem_u32(&sm.ctrl[s]);
-                const uint32_t b = e[s] & 1u, par = (e[s] >> 1) & 1u;
-                const uint32_t a_stat_full = ct_a + offsetof(StreamCtrl, bar_stat_full) + 8 * b;
-                if (!__any_sync(0xFFFFFFFFu, mbar_try_wait_suspend_a(a_stat_full, par, 500))) continue;
-                wait(a_stat_full, par);  // every lane takes the acquire itself
-                progressed = true;
-                const int item = static_cast<int>(lds_u32(ct_a + offsetof(StreamCtrl, stat_item) + 4 * b));
-                if (item < 0) {
-                    done[s] = true;
-                    continue;
-                }
-                const float inv_l = lds_f32(ct_a + offsetof(StreamCtrl, stat_inv_l) + (b * kBlockM + wq * 32 + lane) * 4);
-                wait(ct_a + offsetof(StreamCtrl, bar_o_full) + 8 * b, par);
-                tc_fence_after_sync();
-                // the previous store of this warp must have finished reading the staging tile
-                if (staged && lane == 0) tma_store_wait_read();
-                __syncwarp();
-                const uint32_t o_addr = tmem_q + s * kColsPerStream + kColO + 64u * b;
-                // row `lane` of the warp occupies 128 bytes; its 16-byte chunk j sits at chunk position j ^ (lane & 7)
-                const uint32_t a_row = a_stage + lane * 128;
-#pragma unroll
-                for (int q16 = 0; q16 < 4; ++q16) {
-                    uint32_t o[16];
-                    tmem_ld16(o_addr + q16 * 16, o);
-                    tmem_wait_ld();
-                    uint32_t pk[8];
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const float x = __uint_as_float(o[2 * j]) * inv_l;
-                        const float y = __uint_as_float(o[2 * j + 1]) * inv_l;
-                        // inv_l == 0: the row keeps nothing (its accumulator may hold anything, even NaN)
-                        pk[j] = inv_l == 0.f ? 0u : (kBf16 ? pack_bf16x2(x, y) : pack_f16x2(x, y));
-                    }
-                    sts_v4(a_row + (((2 * q16) ^ (lane & 7)) << 4), make_uint4(pk[0], pk[1], pk[2], pk[3]));
-                    sts_v4(a_row + (((2 * q16 + 1) ^ (lane & 7)) << 4), make_uint4(pk[4], pk[5], pk[6], pk[7]));
-                }
-                tc_fence_before_sync();
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive_a(ct_a + offsetof(StreamCtrl, bar_o_free) + 8 * b);
-                    const int row0 = item_row0(item) + wq * static_cast<int>(kStageRowsOut);
-                    if (row0 < N && ok) {
-                        tma_store_3d(&tmap_o, sm.staging[wq], 0, row0, item_bh(item));
-                        tma_store_commit();
-                    }
-                }
-                staged = true;
-                ++e[s];
-            }
-            if (progressed) {
-                t_idle = clock64();
-            } else {
-                if (*abort_flag) ok = false;
-                if (clock64() - t_idle > kWaitLimitCycles) {
-                    *abort_flag = 1u;
-                    atomicExch(&g_device_status, kDeviceTimeout);
-                    ok = false;
-                }
-            }
-        }
-        if (lane == 0) tma_store_wait_all();
-    } else {
+    {
         const int stream = wg == 0 ? (warp & 1) : (wg - 1);
         StreamTiles& tl = sm.tiles[stream];
         StreamCtrl& ct = sm.ctrl[stream];
@@ -317,20 +292,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         const uint32_t ct_a = smem_u32(&ct);
         const uint32_t a_bar_q = ct_a + offsetof(StreamCtrl, bar_q);
         const uint32_t a_bar_q_free = ct_a + offsetof(StreamCtrl, bar_q_free);
-        const uint32_t a_bar_kv = ct_a + offsetof(StreamCtrl, bar_kv);
+        const uint32_t a_bar_k = ct_a + offsetof(StreamCtrl, bar_k);
+        const uint32_t a_bar_v = ct_a + offsetof(StreamCtrl, bar_v);
         const uint32_t a_bar_pv_done = ct_a + offsetof(StreamCtrl, bar_pv_done);
         const uint32_t a_bar_s_full = ct_a + offsetof(StreamCtrl, bar_s_full);
         const uint32_t a_bar_p_full = ct_a + offsetof(StreamCtrl, bar_p_full);
         const uint32_t a_bar_list_full = ct_a + offsetof(StreamCtrl, bar_list_full);
         const uint32_t a_bar_strip_full = ct_a + offsetof(StreamCtrl, bar_strip_full);
         const uint32_t a_bar_slot_free = ct_a + offsetof(StreamCtrl, bar_slot_free);
-        const uint32_t a_bar_stat_full = ct_a + offsetof(StreamCtrl, bar_stat_full);
         const uint32_t a_bar_o_full = ct_a + offsetof(StreamCtrl, bar_o_full);
         const uint32_t a_bar_o_free = ct_a + offsetof(StreamCtrl, bar_o_free);
         const uint32_t a_desc0 = ct_a + offsetof(StreamCtrl, desc);
         const uint32_t a_strip0 = smem_u32(tl.strip[0]);
         const uint32_t tmem = sm.tmem_base + stream * kColsPerStream;
-        const int first_item = blockIdx.x + stream * gridDim.x;
 
         if (wg != 0) {
             // =========================================== softmax warps ===========================================
@@ -340,12 +314,26 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             const float c = args.scale_log2e;
 
             uint32_t g = 0;                 // key tiles processed by this stream so far (drives the barrier phases)
-            uint32_t sbuf = 0, sphase = 0;  // g % 2 and (g / 2) & 1
+            uint32_t sbuf = 0, sphase = 0;  // g % 3 and (g / 3) & 1
             uint32_t u = 0;                 // chunks consumed so far
             uint32_t r = 0;                 // work items started so far
             float sc[64] = {};              // scores of the tile in work
+            // The end of an item (reading O, normalising, storing) is put off until the first tile of the next item
+            // is done: by then the item's last P V has long completed, and the next item's S is waiting anyway.
+            bool fin_on = false;   // an item is waiting to be finished
+            float fin_inv_l = 0.f; // 1 / row sum of this thread's row of it (0: the row keeps nothing)
+            int fin_item = 0;
+            uint32_t fin_r = 0;    // its ordinal (phase of bar_o_full)
+            const uint32_t a_stage = smem_u32(sm.staging[stream][wq]);
+            auto finish_pending = [&]() {
+                wait(a_bar_o_full, fin_r & 1u);
+                tc_fence_after_sync();
+                const int row0 = item_row0(fin_item) + wq * static_cast<int>(kStageRowsOut);
+                finish_rows<kBf16>(tmem_lane + kColO, fin_inv_l, a_stage, a_bar_o_free, &tmap_o, row0, item_bh(fin_item),
+                                   row0 < N && ok);
+                fin_on = false;
+            };
             for (;;) {
-                const uint32_t ob = r & 1u;  // O accumulator (and row-sum buffer) of this item
                 float m_run = -INFINITY;     // reference max of the unscaled scores (lags the true max by < 8/c)
                 float l_run = 0.f;           // running sum of exp2(c * (s - m_run))
                 int item = -1;
@@ -385,11 +373,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                             tmem_ld32_f32(tmem_lane + kColS + 64u * sbuf + 32, &sc[32]);
                         }
                         // The tile loop is one rolled body (mask + maximum, then exponentials + P) on one register
-                        // set; two tiles per loop body let the compiler overlap the tail of one tile with the head of
-                        // the next.  Longer bodies (the bf16 hi+lo one twice, any one three times) run slower: the
-                        // loop lives at the edge of what instruction fetch sustains.
-                        constexpr int kTileUnroll = kSplitP ? 1 : 2;
-#pragma unroll kTileUnroll
+                        // set, one tile per pass: the loop lives at the edge of what instruction fetch sustains, and
+                        // every unrolled or software-pipelined form that was tried ran slower.
+#pragma unroll 1
                         for (int local = 0; local < count; ++local) {
                             const uint32_t s_col = kColS + 64u * sbuf;  // S of this tile; P goes over the same columns
                             if ((e_cur >> (8 + wq)) & 1u) {
@@ -444,7 +430,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                                     // implies that an earlier tile of this item kept something, so g >= 1)
                                     wait(a_bar_pv_done + 8 * ((g - 1) % kStages), ((g - 1) / kStages) & 1);
                                     tc_fence_after_sync();
-                                    rescale_o_row(tmem_lane + kColO + 64u * ob, alpha);
+                                    rescale_o_row(tmem_lane + kColO, alpha);
                                 }
                             } else {
                                 // none of this warp's rows keeps a key of the tile: P = 0, nothing else changes
@@ -457,10 +443,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                             tmem_wait_st();
                             tc_fence_before_sync();
                             mbar_arrive_a(a_bar_p_full + 8 * sbuf);
+                            if (fin_on) finish_pending();  // the previous item, behind this item's first tile
 
                             ++g;
-                            sbuf ^= 1u;
-                            sphase ^= sbuf ^ 1u;  // flips when sbuf wraps to 0
+                            if (++sbuf == kSBuffers) {
+                                sbuf = 0;
+                                sphase ^= 1u;
+                            }
                             // scores of the next tile into the registers that have just been used up
                             if (local + 1 < count) {
                                 e_cur = lds_u16(a_entries + 2 * (local + 1));
@@ -478,11 +467,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 } while (!last);
                 if (!ok) break;
 
-                // ---- end of the item (or of the stream): hand the row sums to the epilogue warps ----------------
-                // the buffers were last used by item r-2: its epilogue must have read them
-                if (r >= 2) wait(a_bar_o_free + 8 * ob, ((r >> 1) - 1) & 1u);
-                if (item >= 0) {
-                    sts_f32(ct_a + offsetof(StreamCtrl, stat_inv_l) + (ob * kBlockM + stid) * 4, l_run > 0.f ? 1.f / l_run : 0.f);
+                // ---- end of the item (or of the stream) ---------------------------------------------------------
+                if (fin_on) finish_pending();  // an item without tiles in between, or the end of the stream
+                if (item < 0) break;
+                {
                     const int row = item_row0(item) + stid;
                     if (args.save_lse && row < N) {
                         const float kLn2 = 0.6931471805599453f;
@@ -490,145 +478,94 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                             l_run > 0.f ? (fmaf(m_run, c, lg2_approx(l_run)) * kLn2) : -INFINITY;
                     }
                 }
-                if (stid == 0) sts_u32(ct_a + offsetof(StreamCtrl, stat_item) + 4 * ob, static_cast<uint32_t>(item));
-                mbar_arrive_a(a_bar_stat_full + 8 * ob);
-                if (item < 0) break;
+                fin_on = true;
+                fin_inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
+                fin_item = item;
+                fin_r = r;
                 ++r;
             }
+            if (lane == 0) tma_store_wait_all();
         } else {
             setmaxnreg_dec<kRegsOther>();
+            const bool leader = elect_one();  // the lane that issues this warp's single-thread instructions
+            const int leader_lane = __ffs(__ballot_sync(0xFFFFFFFFu, leader)) - 1;
+            // shared by the two helper warps of a stream: tcgen05.mma operand descriptors
+            constexpr uint32_t kInFmt = kBf16 ? kFmtBF16 : kFmtF16;
+            constexpr uint32_t kStageStep = kKVTileBytes >> 4;  // descriptor address units are 16 bytes
+            constexpr uint32_t kQStep = kQTileBytes >> 4;
+            constexpr uint32_t kHi = kSmemDescSw128Hi;
+            static_assert(kStages == kSBuffers, "tile j uses K/V stage j % 3 and S/P buffer j % 3: one counter serves both");
             if (warp < kNumStreams) {
-                // ================================= MMA warp of one stream =================================
+                // ================================= P V warp of one stream =================================
                 // All 32 lanes run the control flow and the address arithmetic (values the compiler can prove to be
-                // warp-uniform stay in uniform registers, where tcgen05.mma wants its operands); lane 0 alone issues.
-                constexpr uint32_t kInFmt = kBf16 ? kFmtBF16 : kFmtF16;
-                const uint32_t idesc_s = make_idesc(kInFmt, kInFmt, kMajorK, kMajorK, kBlockM, kBlockN, args.negate_q);
+                // warp-uniform stay in uniform registers, where tcgen05.mma wants its operands); an elected lane issues.
+                // The warp walks the chunk descriptors and issues O (+)= P V tile by tile, as the softmax threads
+                // publish P.  (S = Q K^T is issued by the loader warp: one thread issuing both took longer per tile
+                // than the softmax threads need, and every tcgen05.mma costs its issuer some 60-80 cycles.)
                 constexpr uint32_t idesc_pv = make_idesc(kInFmt, kInFmt, kMajorK, kMajorMN, kBlockM, kHeadDim, 0);
-                const uint32_t q_lo0 = smem_desc_sw128_lo(smem_u32(tl.q[0]));
-                const uint32_t k_lo0 = smem_desc_sw128_lo(smem_u32(tl.k[0]));
                 const uint32_t v_lo0 = smem_desc_sw128_lo(smem_u32(tl.v[0]));
-                constexpr uint32_t kStageStep = kKVTileBytes >> 4;  // descriptor address units are 16 bytes
-                constexpr uint32_t kQStep = kQTileBytes >> 4;
-                constexpr uint32_t kHi = kSmemDescSw128Hi;
-
-                uint32_t j = 0;    // tiles whose S has been issued
-                uint32_t jp = 0;   // tiles whose P V has been issued; at most one behind j between tiles
-                // per tile in flight (tile ordinal % 4, four bits each): 1 = first tile of its item (P V overwrites O),
-                // 2 = last tile of its item (commit bar_o_full behind its P V), 4 = O accumulator of the item
-                uint32_t tinfo = 0;
-                auto issue_pv = [&]() {  // P V of tile jp
-                    const uint32_t stage = jp % kStages;
-                    const uint32_t pbuf = jp & 1u;
-                    const uint32_t info = (tinfo >> (4 * (jp & 3u))) & 0xFu;
-                    wait(a_bar_p_full + 8 * pbuf, (jp >> 1) & 1u);
-                    tc_fence_after_sync();
-                    const uint32_t v_lo = v_lo0 + stage * kStageStep;
-                    const uint32_t p_addr = tmem + kColS + 64u * pbuf;
-                    const uint32_t o_addr = tmem + kColO + 64u * ((info >> 2) & 1u);
-                    const uint32_t acc = (info & 1u) ^ 1u;
-                    if (lane == 0 && ok) {
-                        // 16 keys = 16 rows of 128 bytes = 2048 bytes of V; 16 P values = 8 tensor-memory columns
-                        mma_ts_lh(o_addr, p_addr, v_lo, kHi, idesc_pv, acc);
-                        if constexpr (kSplitP) mma_ts_lh(o_addr, p_addr + 32, v_lo, kHi, idesc_pv, 1u);
-#pragma unroll
-                        for (int kk = 1; kk < kBlockN / 16; ++kk) {
-                            mma_ts_lh(o_addr, p_addr + 8 * kk, v_lo + 128 * kk, kHi, idesc_pv, 1u);
-                            if constexpr (kSplitP) mma_ts_lh(o_addr, p_addr + 32 + 8 * kk, v_lo + 128 * kk, kHi, idesc_pv, 1u);
-                        }
-                        mma_commit_a(a_bar_pv_done + 8 * stage);
-                        if (info & 2u) mma_commit_a(a_bar_o_full + 8 * ((info >> 2) & 1u));
-                    }
-                    __syncwarp();
-                    ++jp;
-                };
+                const uint32_t o_addr = tmem + kColO;
+                uint32_t pb = 0, pphase = 0;   // (tiles done) % 3 and (tiles done / 3) & 1
                 uint32_t u = 0;  // chunks consumed
                 uint32_t r = 0;  // work items started
-                bool in_item = false;
-                uint32_t item_tiles = 0;
+                uint32_t item_tiles = 0;  // tiles issued for the item in work
                 while (ok) {
                     const uint32_t slot = u & 1u, spar = (u >> 1) & 1u;
-                    if (!__all_sync(0xFFFFFFFFu, mbar_test_wait_a(a_bar_list_full + 8 * slot, spar))) {
-                        // The descriptor is not there yet.  Before blocking, issue what is pending, so that the end
-                        // of the previous item does not wait for the next one to be found.
-                        while (jp < j && ok) issue_pv();
-                        wait(a_bar_list_full + 8 * slot, spar);
-                        if (!ok) break;
-                    }
+                    wait(a_bar_list_full + 8 * slot, spar);
+                    if (!ok) break;
                     const uint32_t a_desc = a_desc0 + slot * 32u;
                     const int item = static_cast<int>(__shfl_sync(0xFFFFFFFFu, lds_u32(a_desc), 0));
                     if (item < 0) break;
                     const uint32_t meta = __shfl_sync(0xFFFFFFFFu, lds_u32(a_desc + 4), 0);
                     const uint32_t count = meta & 0xFFu;
                     const bool last = (meta >> 8) & 1u;
-                    const uint32_t ob = r & 1u, rpar = (r >> 1) & 1u;
-                    if (!in_item) {
-                        in_item = true;
-                        item_tiles = 0;
-                        // O accumulator r % 2 was last used by item r-2: its epilogue must have read it.  That epilogue
-                        // may itself be waiting for a P V that is still pending here (when item r-1 had no tiles), so
-                        // what is pending is issued before this warp blocks.
-                        if (r >= 2 && !__all_sync(0xFFFFFFFFu, mbar_test_wait_a(a_bar_o_free + 8 * ob, rpar ^ 1u))) {
-                            while (jp < j && ok) issue_pv();
-                            wait(a_bar_o_free + 8 * ob, rpar ^ 1u);
-                        }
-                    }
                     for (uint32_t i = 0; i < count && ok; ++i) {
-                        // S(j) goes to buffer j % 2, whose previous tenant P(j-2) was read by P V(j-2), issued before.
-                        const uint32_t stage = j % kStages;
-                        const uint32_t sb = j & 1u;
-                        if (item_tiles == 0) wait(a_bar_q + 8 * ob, rpar);
-                        wait(a_bar_kv + 8 * stage, (j / kStages) & 1u);
+                        wait(a_bar_p_full + 8 * pb, pphase);
+                        // the item's first product overwrites O: the epilogue must have read the previous item's
+                        if (item_tiles == 0 && r >= 1) wait(a_bar_o_free, (r - 1) & 1u);
+                        wait(a_bar_v + 8 * pb, pphase);  // V landed (requested when P V of tile j-3 completed)
                         tc_fence_after_sync();
-                        const uint32_t q_lo = q_lo0 + ob * kQStep;
-                        const uint32_t k_lo = k_lo0 + stage * kStageStep;
-                        const uint32_t s_addr = tmem + kColS + 64u * sb;
-                        if (lane == 0 && ok) {
-                            // 16 elements of the contraction = 32 bytes inside the swizzled 128-byte row
-                            mma_ss_lh(s_addr, q_lo, k_lo, kHi, idesc_s, 0u);
+                        const uint32_t v_lo = v_lo0 + pb * kStageStep;
+                        const uint32_t p_addr = tmem + kColS + 64u * pb;
+                        const uint32_t acc = item_tiles == 0 ? 0u : 1u;
+                        if (leader && ok) {
+                            // 16 keys = 16 rows of 128 bytes = 2048 bytes of V; 16 P values = 8 tensor-memory columns
+                            mma_ts_lh(o_addr, p_addr, v_lo, kHi, idesc_pv, acc);
+                            if constexpr (kSplitP) mma_ts_lh(o_addr, p_addr + 32, v_lo, kHi, idesc_pv, 1u);
 #pragma unroll
-                            for (int kk = 1; kk < kHeadDim / 16; ++kk) mma_ss_lh(s_addr, q_lo + 2 * kk, k_lo + 2 * kk, kHi, idesc_s, 1u);
-                            mma_commit_a(a_bar_s_full + 8 * sb);
+                            for (int kk = 1; kk < kBlockN / 16; ++kk) {
+                                mma_ts_lh(o_addr, p_addr + 8 * kk, v_lo + 128 * kk, kHi, idesc_pv, 1u);
+                                if constexpr (kSplitP) mma_ts_lh(o_addr, p_addr + 32 + 8 * kk, v_lo + 128 * kk, kHi, idesc_pv, 1u);
+                            }
+                            mma_commit_a(a_bar_pv_done + 8 * pb);
+                            if (last && i + 1 == count) mma_commit_a(a_bar_o_full);
                         }
                         __syncwarp();
-                        const uint32_t info = (item_tiles == 0 ? 1u : 0u) | ((last && i + 1 == count) ? 2u : 0u) | (ob << 2);
-                        tinfo = (tinfo & ~(0xFu << (4 * (j & 3u)))) | (info << (4 * (j & 3u)));
-                        ++j;
                         ++item_tiles;
-                        if (j - jp > 1) issue_pv();  // P V of the tile before the one just issued
+                        if (++pb == kSBuffers) {
+                            pb = 0;
+                            pphase ^= 1u;
+                        }
                     }
-                    if (lane == 0) mbar_arrive_a(a_bar_slot_free + 8 * slot);
+                    if (leader) mbar_arrive_a(a_bar_slot_free + 8 * slot);
                     __syncwarp();
                     ++u;
                     if (last) {
-                        // ---- end of the item: its Q tile and (behind the last P V) its O accumulator are complete ----
-                        if (item_tiles == 0) {
-                            // nothing was issued for this item; its Q tile was requested all the same and must have
-                            // landed before the buffer is declared free
-                            wait(a_bar_q + 8 * ob, rpar);
+                        // ---- end of the item.  bar_o_full has one phase per item; when the item's last tile was not
+                        // in its final chunk (or the item has no tile at all) the commit comes here.  It may only move
+                        // on once the epilogue has passed the previous item's phase.
+                        if (count == 0) {
+                            if (item_tiles == 0 && r >= 1) wait(a_bar_o_free, (r - 1) & 1u);
+                            if (leader && ok) mma_commit_a(a_bar_o_full);
+                            __syncwarp();
                         }
-                        bool commit_o_now = true;
-                        if (item_tiles > 0 && (tinfo >> (4 * ((j - 1) & 3u)) & 2u) == 0u) {
-                            // the final chunk was empty: the item's last tile is the newest one
-                            if (jp < j) {
-                                tinfo |= 2u << (4 * ((j - 1) & 3u));  // its P V is still to come: commit behind it
-                                commit_o_now = false;
-                            }
-                        } else if (item_tiles > 0) {
-                            commit_o_now = false;  // marked when the tile was issued
-                        }
-                        if (lane == 0 && ok) {
-                            mma_commit_a(a_bar_q_free + 8 * ob);
-                            if (commit_o_now) mma_commit_a(a_bar_o_full + 8 * ob);
-                        }
-                        __syncwarp();
-                        in_item = false;
+                        item_tiles = 0;
                         ++r;
                     }
                 }
-                while (jp < j && ok) issue_pv();
             } else {
-                // ================================ loader warp of one stream ================================
-                if (lane == 0) {
+                // ======================== loader warp of one stream (also issues S = Q K^T) ========================
+                if (leader) {
                     tma_prefetch_desc(&tmap_q);
                     tma_prefetch_desc(&tmap_k);
                     tma_prefetch_desc(&tmap_v);
@@ -637,12 +574,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 const uint32_t tail_bits = (N & 31) ? ((1u << (N & 31)) - 1u) : 0xFFFFFFFFu;
                 const uint32_t q_a0 = smem_u32(tl.q[0]), k_a0 = smem_u32(tl.k[0]), v_a0 = smem_u32(tl.v[0]);
                 const bool mask_tma = args.mask_tma != 0;
+                const uint32_t idesc_s = make_idesc(kInFmt, kInFmt, kMajorK, kMajorK, kBlockM, kBlockN, args.negate_q);
+                const uint32_t q_lo0 = smem_desc_sw128_lo(q_a0);
+                const uint32_t k_lo0 = smem_desc_sw128_lo(k_a0);
 
                 // The strip of chunk `c` of a work item: rows row0..row0+127, words 16c..16c+15 of each row, zeros
                 // outside the mask.  With a tensor map it is one TMA tile copy that completes on bar_strip_full;
                 // otherwise the warp copies it with plain loads (and the caller arrives on the barrier).
                 auto strip_tma = [&](uint32_t slot, int item, int c) {
-                    if (lane == 0 && ok) {
+                    if (leader && ok) {
                         const uint32_t bar = a_bar_strip_full + 8 * slot;
                         mbar_arrive_expect_tx_a(bar, kStripBytes);
                         tma_load_3d_a(a_strip0 + slot * kStripBytes, &tmap_m, bar, c * kChunkWords, item_row0(item), item_bh(item));
@@ -671,19 +611,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 // Non-empty tiles of the chunk whose strip sits in `slot`, written into the slot's descriptor; returns
                 // their number.  Lane l looks at rows l, 32+l, 64+l, 96+l.
                 auto list_from_strip = [&](uint32_t slot, int c) -> uint32_t {
-                    const uint32_t a_strip = a_strip0 + slot * kStripBytes;
+                    const uint4* strip = reinterpret_cast<const uint4*>(tl.strip[slot]);
                     uint32_t grp[4];
 #pragma unroll
-                    for (int gq = 0; gq < 4; ++gq) {
-                        const uint32_t a_row = a_strip + (gq * 32 + lane) * kStripRowBytes;
-                        uint32_t mine = 0;
+                    for (int half = 0; half < 2; ++half) {
+                        uint4 x[8];  // two row groups at a time: eight loads in flight
 #pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            const uint4 x = lds_v4(a_row + 16 * k);
-                            if ((x.x | x.y) != 0u) mine |= 1u << (2 * k);
-                            if ((x.z | x.w) != 0u) mine |= 2u << (2 * k);
+                        for (int i = 0; i < 8; ++i)
+                            x[i] = strip[((2 * half + (i >> 2)) * 32 + lane) * (kStripRowBytes / 16) + (i & 3)];
+#pragma unroll
+                        for (int gq = 0; gq < 2; ++gq) {
+                            uint32_t mine = 0;
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                if ((x[4 * gq + k].x | x[4 * gq + k].y) != 0u) mine |= 1u << (2 * k);
+                                if ((x[4 * gq + k].z | x[4 * gq + k].w) != 0u) mine |= 2u << (2 * k);
+                            }
+                            grp[2 * half + gq] = __reduce_or_sync(0xFFFFFFFFu, mine);
                         }
-                        grp[gq] = __reduce_or_sync(0xFFFFFFFFu, mine);
                     }
                     const uint32_t any = grp[0] | grp[1] | grp[2] | grp[3];
                     if (lane < kChunkTiles && ((any >> lane) & 1u)) {
@@ -696,63 +641,143 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 };
 
                 uint32_t u = 0;  // chunks published
-                uint32_t j = 0;  // tiles of this stream whose K/V loads have been issued
+                uint32_t j = 0;  // tiles of this stream whose K load has been issued
+                uint32_t ls = 0, lph = 0;  // j % 3 and (j / 3) & 1
+                uint32_t js = 0;           // tiles whose V load and S product have been issued (js == j or j - 1)
+                uint32_t ss = 0, sph = 0;  // js % 3 and (js / 3) & 1
                 uint32_t r = 0;  // work items started
-                bool pre = false;  // the strip of chunk u has already been requested (early, from the K/V loop)
-                auto wait_slot_free = [&](uint32_t un) {
-                    if (un >= kSlots) wait(a_bar_slot_free + 8 * (un & 1u), ((un >> 1) - 1) & 1u);
+                bool pre = false;  // the strip of chunk u has already been requested (early, from the K loop)
+                // The K and V tiles of a key tile travel separately, because they are needed at different times.  S(j)
+                // should be complete two tiles before the softmax threads get to tile j, so K(j) is requested as soon as
+                // its ring stage is free, which is when S(j-3) has completed.  V(j) is needed only after the softmax
+                // threads have finished tile j; its stage and the S/P buffer j % 3 become free together, when P V(j-3)
+                // completes, and at that moment this warp requests V(j) and issues S(j), whose K tile landed a tile
+                // ago.  Loads therefore never sit on the path from "P(j-3) published" to "S(j) complete".
+                // What the V load and the S product of the tile whose K was requested last need to know:
+                bool pend = false;        // such a tile exists (then js == j - 1)
+                bool pend_first = false;  // first tile of its item: the item's Q tile must have landed
+                bool pend_last = false;   // last tile of its item: behind it the Q buffer is free again
+                uint32_t pend_r = 0;      // ordinal of its item
+                int pend_t = 0, pend_bh = 0;  // its key tile and batch*head
+                bool pend_first_of_item = false;  // the next tile to be loaded is the first of its item
+                auto issue_s = [&]() {  // V load and S product of the pending tile (S/P buffer and ring stage ss)
+                    // buffer and stage are free when P V of their previous tenant (tile js-3) has completed: that product
+                    // read P(js-3) and V(js-3)
+                    if (js >= kStages) wait(a_bar_pv_done + 8 * ss, sph ^ 1u);
+                    // after a failed wait nothing more is loaded or issued: the buffers may still be in use
+                    if (leader && ok) {
+                        const uint32_t bar = a_bar_v + 8 * ss;
+                        mbar_arrive_expect_tx_a(bar, kKVTileBytes);
+                        tma_load_3d_a(v_a0 + ss * kKVTileBytes, &tmap_v, bar, 0, pend_t * kBlockN, pend_bh);
+                    }
+                    __syncwarp();
+                    const uint32_t qb = pend_r & 1u;
+                    if (pend_first) wait(a_bar_q + 8 * qb, (pend_r >> 1) & 1u);
+                    wait(a_bar_k + 8 * ss, sph);
+                    tc_fence_after_sync();
+                    const uint32_t q_lo = q_lo0 + qb * kQStep;
+                    const uint32_t k_lo = k_lo0 + ss * kStageStep;
+                    const uint32_t s_addr = tmem + kColS + 64u * ss;
+                    if (leader && ok) {
+                        // 16 elements of the contraction = 32 bytes inside the swizzled 128-byte row
+                        mma_ss_lh(s_addr, q_lo, k_lo, kHi, idesc_s, 0u);
+#pragma unroll
+                        for (int kk = 1; kk < kHeadDim / 16; ++kk) mma_ss_lh(s_addr, q_lo + 2 * kk, k_lo + 2 * kk, kHi, idesc_s, 1u);
+                        mma_commit_a(a_bar_s_full + 8 * ss);
+                        if (pend_last) mma_commit_a(a_bar_q_free + 8 * qb);
+                    }
+                    __syncwarp();
+                    ++js;
+                    if (++ss == kSBuffers) {
+                        ss = 0;
+                        sph ^= 1u;
+                    }
+                    pend = false;
                 };
-                // K/V loads of the tiles listed in `slot` (for item bh), each as soon as its ring stage is free.  While
-                // waiting, the strip of the following chunk (item_n, c_n) is requested as soon as its slot is free.
-                auto issue_kv = [&](uint32_t slot, uint32_t count, int bh, bool have_n, int item_n, int c_n) {
+                // the same, if nothing it needs is still outstanding (never blocks)
+                auto try_issue_s = [&]() {
+                    if (pend && __all_sync(0xFFFFFFFFu, mbar_test_wait_a(a_bar_k + 8 * ss, sph) &&
+                                                            (js < kStages || mbar_test_wait_a(a_bar_pv_done + 8 * ss, sph ^ 1u))))
+                        issue_s();
+                };
+                // Waits until the consumers have left the chunk that used the slot of chunk `un`.  They cannot leave a
+                // chunk whose last S product is still pending here, so that one is issued before this warp blocks.
+                auto wait_slot_free = [&](uint32_t un) {
+                    if (un < kSlots) return;
+                    const uint32_t bar = a_bar_slot_free + 8 * (un & 1u), par = ((un >> 1) - 1) & 1u;
+                    if (pend && !__all_sync(0xFFFFFFFFu, mbar_test_wait_a(bar, par))) issue_s();
+                    wait(bar, par);
+                };
+                // K loads of the tiles listed in `slot` (for item bh), each as soon as its ring stage is free, and behind
+                // each the V load and the S product of the tile before.  While waiting, the strip of the following chunk
+                // (item_n, c_n) is requested as soon as its slot is free.
+                auto issue_kv = [&](uint32_t slot, uint32_t count, bool last, int bh, bool have_n, int item_n, int c_n) {
                     const uint32_t a_entries = a_desc0 + slot * 32u + 8;
                     for (uint32_t i = 0; i < count && ok; ++i) {
                         const int t = static_cast<int>(__shfl_sync(0xFFFFFFFFu, lds_u16(a_entries + 2 * i), 0) & 0xFFu);
-                        const uint32_t stage = j % kStages;
                         if (!kPlanned && mask_tma && have_n && !pre) {
                             const uint32_t un = u + 1;
                             if (un < kSlots ||
                                 __all_sync(0xFFFFFFFFu, mbar_test_wait_a(a_bar_slot_free + 8 * (un & 1u), ((un >> 1) - 1) & 1u))) {
-                                wait_slot_free(un);  // returns at once; every lane takes the acquire itself
                                 strip_tma(un & 1u, item_n, c_n);
                                 pre = true;
                             }
                         }
-                        // Tile ordinal j uses stage j % 3 of the K/V ring.  A stage is reloaded when P V of its previous
-                        // tenant (tile j-3) has completed, which also covers that tile's S.
-                        if (j >= kStages) wait(a_bar_pv_done + 8 * stage, ((j / kStages) - 1) & 1u);
-                        // after a failed wait nothing more is loaded: the buffers may still be in use
-                        if (lane == 0 && ok) {
-                            const uint32_t bar = a_bar_kv + 8 * stage;
-                            mbar_arrive_expect_tx_a(bar, 2 * kKVTileBytes);
-                            tma_load_3d_a(k_a0 + stage * kKVTileBytes, &tmap_k, bar, 0, t * kBlockN, bh);
-                            tma_load_3d_a(v_a0 + stage * kKVTileBytes, &tmap_v, bar, 0, t * kBlockN, bh);
+                        // Tile ordinal j uses stage j % 3 of the K ring, free when S(j-3) has completed (issued two steps ago)
+                        if (j >= kStages) wait(a_bar_s_full + 8 * ls, lph ^ 1u);
+                        if (leader && ok) {
+                            const uint32_t bar = a_bar_k + 8 * ls;
+                            mbar_arrive_expect_tx_a(bar, kKVTileBytes);
+                            tma_load_3d_a(k_a0 + ls * kKVTileBytes, &tmap_k, bar, 0, t * kBlockN, bh);
                         }
                         __syncwarp();
+                        if (pend) issue_s();
+                        pend = true;
+                        pend_first = i == 0 && pend_first_of_item;
+                        pend_last = last && i + 1 == count;
+                        pend_r = r;
+                        pend_t = t;
+                        pend_bh = bh;
+                        if (i == 0) pend_first_of_item = false;
                         ++j;
+                        if (++ls == kStages) {
+                            ls = 0;
+                            lph ^= 1u;
+                        }
                     }
                 };
                 auto publish = [&](uint32_t slot, int item, uint32_t count, bool last) {
-                    if (lane == 0) {
+                    if (leader) {
                         sts_u32(a_desc0 + slot * 32u, static_cast<uint32_t>(item));
                         sts_u32(a_desc0 + slot * 32u + 4, count | (last ? 0x100u : 0u));
                     }
                     __syncwarp();
-                    if (lane == 0) mbar_arrive_a(a_bar_list_full + 8 * slot);
+                    if (leader) mbar_arrive_a(a_bar_list_full + 8 * slot);
                     __syncwarp();
                 };
-
-                for (int item = first_item; item < total_items && ok; item += item_stride, ++r) {
+                // next work item of this CTA for this stream, or -1 when all have been taken
+                auto take_item = [&]() -> int {
+                    uint32_t k = 0;
+                    if (leader) k = atomicAdd(&sm.next_item, 1u);
+                    k = __shfl_sync(0xFFFFFFFFu, k, leader_lane);
+                    const long long it = static_cast<long long>(blockIdx.x) + static_cast<long long>(k) * gridDim.x;
+                    return it < total_items ? static_cast<int>(it) : -1;
+                };
+                int item_next = take_item();
+                while (item_next >= 0 && ok) {
+                    const int item = item_next;
+                    item_next = take_item();  // taken one item ahead: its first mask strip is requested early
                     const int bh = item_bh(item);
-                    const int item_next = item + item_stride;
                     // Q tile into buffer r % 2, last used by item r-2: all its S products must be complete
                     if (r >= 2) wait(a_bar_q_free + 8 * (r & 1u), ((r >> 1) - 1) & 1u);
-                    if (lane == 0 && ok) {
+                    if (leader && ok) {
                         const uint32_t bar = a_bar_q + 8 * (r & 1u);
                         mbar_arrive_expect_tx_a(bar, kQTileBytes);
                         tma_load_3d_a(q_a0 + (r & 1u) * kQTileBytes, &tmap_q, bar, 0, item_row0(item), bh);
                     }
                     __syncwarp();
+                    pend_first_of_item = true;
+                    bool item_has_tiles = false, last_marked = false;
                     if constexpr (kPlanned) {
                         // the item's list was computed ahead: count word, then 16-bit entries in ascending tile order;
                         // one chunk descriptor per chunk that holds tiles (one empty descriptor for an empty item)
@@ -774,15 +799,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                                     strip_tma(slot, item, c);
                                 } else {
                                     strip_copy(slot, item, c);
-                                    if (lane == 0) mbar_arrive_a(a_bar_strip_full + 8 * slot);
+                                    if (leader) mbar_arrive_a(a_bar_strip_full + 8 * slot);
                                 }
-                            } else if (lane == 0) {
+                            } else if (leader) {
                                 mbar_arrive_a(a_bar_strip_full + 8 * slot);  // no strip: keep the barrier's phase in step
                             }
                             __syncwarp();
                             pos += count;
-                            publish(slot, item, count, pos >= total);
-                            issue_kv(slot, count, bh, false, 0, 0);
+                            const bool last = pos >= total;
+                            publish(slot, item, count, last);
+                            issue_kv(slot, count, last, bh, false, 0, 0);
+                            item_has_tiles |= count > 0;
+                            last_marked = last && count > 0;
                             ++u;
                         } while (pos < total && ok);
                     } else {
@@ -793,22 +821,37 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                                 if (mask_tma) strip_tma(slot, item, c);
                             }
                             pre = false;
+                            try_issue_s();
                             if (mask_tma) {
                                 wait(a_bar_strip_full + 8 * slot, (u >> 1) & 1u);
                             } else {
                                 strip_copy(slot, item, c);
-                                if (lane == 0) mbar_arrive_a(a_bar_strip_full + 8 * slot);
+                                if (leader) mbar_arrive_a(a_bar_strip_full + 8 * slot);
                                 __syncwarp();
                             }
                             const uint32_t count = list_from_strip(slot, c);
                             const bool last = c + 1 == num_chunks;
                             publish(slot, item, count, last);
-                            const bool have_n = !last || item_next < total_items;
-                            issue_kv(slot, count, bh, have_n, last ? item_next : item, last ? 0 : c + 1);
+                            const bool have_n = !last || item_next >= 0;
+                            issue_kv(slot, count, last, bh, have_n, last ? item_next : item, last ? 0 : c + 1);
+                            item_has_tiles |= count > 0;
+                            last_marked = last && count > 0;
                             ++u;
                         }
                     }
+                    // ---- end of the item on the S side: behind its last S product its Q buffer is free again.  When that
+                    // tile could not be marked (the final chunk was empty) the commit comes here, behind everything issued.
+                    if (!last_marked) {
+                        if (pend) issue_s();
+                        // an item without tiles never waited for its Q tile, which must have landed before the buffer
+                        // is declared free
+                        if (!item_has_tiles) wait(a_bar_q + 8 * (r & 1u), (r >> 1) & 1u);
+                        if (leader && ok) mma_commit_a(a_bar_q_free + 8 * (r & 1u));
+                        __syncwarp();
+                    }
+                    ++r;
                 }
+                if (pend && ok) issue_s();
                 // end of the stream: a descriptor without a work item
                 if (ok) {
                     wait_slot_free(u);

@@ -24,6 +24,22 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// One lane of the (converged) warp, chosen by the hardware.  A single-thread instruction (tcgen05.mma,
+// tcgen05.commit, a TMA copy, mbarrier.arrive.expect_tx) guarded by this predicate is issued from the uniform
+// datapath; guarded by `lane == 0` the same instructions cost their warp half as much again (measured: four
+// tcgen05.mma and a commit take 173 cycles against 272).
+__device__ __forceinline__ bool elect_one() {
+    uint32_t p;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred px;\n\t"
+        "elect.sync _|px, 0xFFFFFFFF;\n\t"
+        "selp.u32 %0, 1, 0, px;\n\t"
+        "}\n"
+        : "=r"(p));
+    return p != 0;
+}
+
 // Programmatic dependent launch: a kernel launched with programmatic stream serialisation may start while its
 // predecessor in the stream is still running.  grid_dependency_wait() returns once the predecessor has completed
 // and its writes are visible; it must precede the first access to global memory.  grid_launch_dependents() lets
@@ -102,8 +118,9 @@ __device__ __forceinline__ bool mbar_try_wait_suspend_a(uint32_t bar, uint32_t p
 // for the whole hint.
 constexpr long long kWaitLimitCycles = 1ll << 32;
 constexpr uint32_t kSuspendHintNs = 20000;
-__device__ __forceinline__ bool mbar_wait_a(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
-    if (mbar_try_wait_a(bar, parity)) return true;
+// The polling loop of a wait whose first test failed.  (Inlined: as an out-of-line call it needs the calling
+// convention's registers, which the softmax warps of the attention kernel, at their register cap, do not have.)
+__device__ __forceinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
     const long long t0 = clock64();
     for (;;) {
         if (mbar_try_wait_suspend_a(bar, parity, kSuspendHintNs)) return true;
@@ -113,6 +130,10 @@ __device__ __forceinline__ bool mbar_wait_a(uint32_t bar, uint32_t parity, volat
     *abort_flag = 1u;
     atomicExch(&g_device_status, kDeviceTimeout);
     return false;
+}
+__device__ __forceinline__ bool mbar_wait_a(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
+    if (mbar_try_wait_a(bar, parity)) return true;
+    return mbar_wait_poll(bar, parity, abort_flag);
 }
 
 // ------------------------------------------------------------------------------------------------
