@@ -37,6 +37,8 @@
 
 #include <stddef.h>
 
+#include <type_traits>
+
 #include "sma_common.cuh"
 
 namespace sma {
@@ -114,6 +116,11 @@ struct AttnSmem {
     uint32_t tmem_base;
     uint32_t abort_flag;  // raised by the first bounded wait that runs out
     uint32_t next_item;   // how many of the CTA's work items its two streams have taken
+    // Turn-taking of the two softmax warps that share a warp scheduler (quadrant q of stream 0 and of stream 1), see
+    // the exponentials in the softmax loop.  bar_turn[q][s]: 1 arrival, "warp (s, q) may run its exponentials".
+    alignas(8) uint64_t bar_turn[4][kNumStreams];
+    uint32_t turn_alive[4][kNumStreams];  // 0 once warp (s, q) has left the softmax loop for good
+    uint32_t first_count[kNumStreams];    // tiles in the first chunk a stream's loader published (~0u: not yet known)
 };
 
 constexpr size_t attn_smem_bytes() { return sizeof(AttnSmem) + 1024; }  // + slack to align the base to 1024
@@ -254,6 +261,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         if (wg == 1) {
             sm.abort_flag = 0u;
             sm.next_item = 0u;
+            sm.first_count[0] = sm.first_count[1] = ~0u;
+            for (int q = 0; q < 4; ++q) {
+                for (int st = 0; st < kNumStreams; ++st) {
+                    mbar_init(&sm.bar_turn[q][st], 1);
+                    sm.turn_alive[q][st] = 1u;
+                }
+                mbar_arrive_a(smem_u32(&sm.bar_turn[q][0]));  // stream 0 begins
+            }
         }
         mbar_init_fence();
     }
@@ -313,6 +328,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             const uint32_t tmem_lane = tmem + (static_cast<uint32_t>(wq * 32) << 16);
             const float c = args.scale_log2e;
 
+            // Turn-taking with the other stream's warp on this warp's scheduler (same lane quadrant), kTurns.  The
+            // scheduler favours the warp with the lower index whenever both are ready, so on a dense mask stream 0 ran a
+            // fifth faster than stream 1, took the same number of work items and then sat idle at the end of the kernel;
+            // and the two warps tend to run their exponentials (special-function pipe) at the same time and their masking
+            // (ALU pipe) at the same time.  Taking turns at the exponentials keeps the two streams in step and puts one
+            // warp's masking and waiting under the other's exponentials: 8 % at the dense headline workload.  Where the
+            // work items differ in length (block-sparse, causal masks) it costs 4-16 % instead, so the CTA decides once,
+            // when both loaders have published their first chunk: turns are taken if work items are a single chunk
+            // (N <= 512: few items per stream, where an uneven finish weighs most) and both first chunks are full of
+            // tiles.  The loop exists in both forms (it is too sensitive to the size of its body to carry the other
+            // form's code).
+            // One turn exists per pair of warps: it sits, as a completed phase, on the barrier of the warp whose turn it
+            // is; a warp takes its turn only while the other one is still in the loop and hands a turn it holds back
+            // when it leaves, so nobody waits for a warp that is gone.
+            auto softmax_role = [&](auto turns_tag) {
+            constexpr bool kTurns = decltype(turns_tag)::value;
             uint32_t g = 0;                 // key tiles processed by this stream so far (drives the barrier phases)
             uint32_t sbuf = 0, sphase = 0;  // g % 3 and (g / 3) & 1
             uint32_t u = 0;                 // chunks consumed so far
@@ -325,8 +356,46 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             int fin_item = 0;
             uint32_t fin_r = 0;    // its ordinal (phase of bar_o_full)
             const uint32_t a_stage = smem_u32(sm.staging[stream][wq]);
+            const uint32_t a_my_turn = smem_u32(&sm.bar_turn[wq][stream]);
+            const uint32_t a_other_turn = smem_u32(&sm.bar_turn[wq][stream ^ 1]);
+            volatile uint32_t* const other_alive = &sm.turn_alive[wq][stream ^ 1];
+            uint32_t turns = 0;  // turns taken so far (phase of bar_turn[wq][stream])
+            // hands a turn this warp holds but does not need right now to the other warp
+            auto pass_turn_on = [&]() {
+                if constexpr (kTurns) {
+                    if (*other_alive && __all_sync(0xFFFFFFFFu, mbar_test_wait_a(a_my_turn, turns & 1u))) {
+                        ++turns;
+                        if (lane == 0) mbar_arrive_a(a_other_turn);
+                    }
+                }
+            };
+            // A wait of a softmax warp for its own stream's progress.  That progress needs all four softmax warps of
+            // the stream, and another one of them may be waiting for a turn that the other stream's warp holds while
+            // it waits, in the same way, for a turn held here.  A warp therefore never sits on a turn while it waits:
+            // whatever turn it holds, or is handed while it polls, goes straight back.
+            auto swait = [&](uint32_t bar, uint32_t parity) {
+                if constexpr (!kTurns) {
+                    wait(bar, parity);
+                    return;
+                }
+                if (!ok || mbar_try_wait_a(bar, parity)) return;
+                const long long t0 = clock64();
+                for (;;) {
+                    pass_turn_on();
+                    if (__all_sync(0xFFFFFFFFu, mbar_try_wait_suspend_a(bar, parity, 1000))) return;
+                    const bool out_of_time = clock64() - t0 > kWaitLimitCycles;
+                    if (__any_sync(0xFFFFFFFFu, *abort_flag != 0u || out_of_time)) {
+                        if (out_of_time) {
+                            *abort_flag = 1u;
+                            atomicExch(&g_device_status, kDeviceTimeout);
+                        }
+                        ok = false;
+                        return;
+                    }
+                }
+            };
             auto finish_pending = [&]() {
-                wait(a_bar_o_full, fin_r & 1u);
+                swait(a_bar_o_full, fin_r & 1u);
                 tc_fence_after_sync();
                 const int row0 = item_row0(fin_item) + wq * static_cast<int>(kStageRowsOut);
                 finish_rows<kBf16>(tmem_lane + kColO, fin_inv_l, a_stage, a_bar_o_free, &tmap_o, row0, item_bh(fin_item),
@@ -352,7 +421,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 };
                 do {
                     const uint32_t slot = u & 1u, spar = (u >> 1) & 1u;
-                    wait(a_bar_list_full + 8 * slot, spar);
+                    swait(a_bar_list_full + 8 * slot, spar);
                     if (!ok) break;
                     const uint32_t a_desc = a_desc0 + slot * 32u;
                     item = static_cast<int>(lds_u32(a_desc));
@@ -362,11 +431,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                     last = (meta >> 8) & 1u;
                     const uint32_t a_entries = a_desc + 8;
                     if (count > 0) {
-                        wait(a_bar_strip_full + 8 * slot, spar);
+                        swait(a_bar_strip_full + 8 * slot, spar);
                         const uint32_t a_row = a_strip0 + slot * kStripBytes + stid * kStripRowBytes;
                         // entry of the tile in work; `has`: this warp's 32 rows keep something in it
                         uint32_t e_cur = lds_u16(a_entries);
-                        wait(a_bar_s_full + 8 * sbuf, sphase);
+                        swait(a_bar_s_full + 8 * sbuf, sphase);
                         tc_fence_after_sync();
                         if ((e_cur >> (8 + wq)) & 1u) {
                             tmem_ld32_f32(tmem_lane + kColS + 64u * sbuf, &sc[0]);
@@ -392,6 +461,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                                 }
                                 float neg_mc;
                                 const float alpha = advance_max(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), neg_mc);
+                                if constexpr (kTurns) {
+                                    if (*other_alive) {
+                                        wait(a_my_turn, turns & 1u);
+                                        ++turns;
+                                    }
+                                }
                                 // packed two-lane fp32 arithmetic (one instruction per pair of scores) for the scaling and the row sum
                                 const uint64_t c2 = pack_f32x2(c, c), neg_mc2 = pack_f32x2(neg_mc, neg_mc);
                                 uint64_t ls2[4] = {0ull, 0ull, 0ull, 0ull};
@@ -420,6 +495,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                                     tmem_st16(tmem_lane + s_col + half * 16, pk);
                                     if constexpr (kSplitP) tmem_st16(tmem_lane + s_col + 32 + half * 16, pk_lo);
                                 }
+                                if constexpr (kTurns) {
+                                    __syncwarp();
+                                    if (lane == 0) mbar_arrive_a(a_other_turn);  // the other warp's turn
+                                }
                                 float l_even, l_odd;
                                 unpack_f32x2(add_f32x2(add_f32x2(ls2[0], ls2[1]), add_f32x2(ls2[2], ls2[3])), l_even, l_odd);
                                 l_run = fmaf(l_run, alpha, l_even + l_odd);
@@ -428,12 +507,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                                 if (__any_sync(0xFFFFFFFFu, alpha != 1.f)) {
                                     // every P V issued so far must have landed in O: the newest one is tile g-1 (alpha != 1
                                     // implies that an earlier tile of this item kept something, so g >= 1)
-                                    wait(a_bar_pv_done + 8 * ((g - 1) % kStages), ((g - 1) / kStages) & 1);
+                                    swait(a_bar_pv_done + 8 * ((g - 1) % kStages), ((g - 1) / kStages) & 1);
                                     tc_fence_after_sync();
                                     rescale_o_row(tmem_lane + kColO, alpha);
                                 }
                             } else {
-                                // none of this warp's rows keeps a key of the tile: P = 0, nothing else changes
+                                // none of this warp's rows keeps a key of the tile: P = 0, nothing else changes; a turn at
+                                // the exponentials that this warp holds goes straight back
+                                pass_turn_on();
                                 uint32_t z[32];
 #pragma unroll
                                 for (int j = 0; j < 32; ++j) z[j] = 0u;
@@ -453,7 +534,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                             // scores of the next tile into the registers that have just been used up
                             if (local + 1 < count) {
                                 e_cur = lds_u16(a_entries + 2 * (local + 1));
-                                wait(a_bar_s_full + 8 * sbuf, sphase);
+                                swait(a_bar_s_full + 8 * sbuf, sphase);
                                 tc_fence_after_sync();
                                 if ((e_cur >> (8 + wq)) & 1u) {
                                     tmem_ld32_f32(tmem_lane + kColS + 64u * sbuf, &sc[0]);
@@ -484,7 +565,28 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 fin_r = r;
                 ++r;
             }
-            if (lane == 0) tma_store_wait_all();
+            // leaving for good: a turn this warp holds goes back to the other one
+            __syncwarp();
+            if (lane == 0) {
+                if constexpr (kTurns) {
+                    sm.turn_alive[wq][stream] = 0u;
+                    __threadfence_block();
+                    if (mbar_test_wait_a(a_my_turn, turns & 1u)) mbar_arrive_a(a_other_turn);
+                }
+                tma_store_wait_all();
+            }
+            };
+            bool take_turns = false;
+            {
+                volatile uint32_t* const fc = sm.first_count;
+                const long long t0 = clock64();
+                while ((fc[0] == ~0u || fc[1] == ~0u) && *abort_flag == 0u && clock64() - t0 < kWaitLimitCycles) __nanosleep(64);
+                take_turns = __all_sync(0xFFFFFFFFu, num_chunks == 1 && fc[0] == kChunkTiles && fc[1] == kChunkTiles);
+            }
+            if (take_turns)
+                softmax_role(std::true_type{});
+            else
+                softmax_role(std::false_type{});
         } else {
             setmaxnreg_dec<kRegsOther>();
             const bool leader = elect_one();  // the lane that issues this warp's single-thread instructions
@@ -750,6 +852,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                     if (leader) {
                         sts_u32(a_desc0 + slot * 32u, static_cast<uint32_t>(item));
                         sts_u32(a_desc0 + slot * 32u + 4, count | (last ? 0x100u : 0u));
+                        if (u == 0) sm.first_count[stream] = item >= 0 ? count : 0u;  // the softmax warps' cue
                     }
                     __syncwarp();
                     if (leader) mbar_arrive_a(a_bar_list_full + 8 * slot);
