@@ -114,6 +114,16 @@ int sma_pack_mask(const uint8_t* mask, uint32_t* packed, int32_t B, int32_t H, i
 int sma_attention_fwd(const sma_attention_params* params, void* stream);
 
 /*
+ * Mask packing and the forward pass behind one call: packs `mask` into params->mask_packed (the caller's buffer,
+ * [B, H, N, ceil(N/32)] uint32, every word written) and runs sma_attention_fwd on it, both on `stream`, in that
+ * order.  Same results as the two calls made one after the other; what it saves is one trip through the caller's
+ * foreign-function layer per step, which for a headline-sized batch costs as much host time as the kernels run.
+ * Replaces: the pair pack_mask() + forward() that the reference's Python layer issues for every call of
+ * sparse_attention() (python/sparse_attention.py:139-146, 64 and 170-171; csrc/binding.cpp:9-66).
+ */
+int sma_sparse_attention_fwd(const sma_attention_params* params, const uint8_t* mask, void* stream);
+
+/*
  * The same forward pass for long, sparse sequences, with a workspace.
  * sma_attention_fwd finds the non-empty 64-key tiles of each block of 128 query rows inside the attention
  * kernel, one warp reading that block's packed-mask rows; beyond a thousand keys or so, and when most tiles are

@@ -41,6 +41,7 @@ EXPORTED_SYMBOLS = (
     "sma_last_cuda_error",
     "sma_pack_mask",
     "sma_attention_fwd",
+    "sma_sparse_attention_fwd",
     "sma_attention_workspace_bytes",
     "sma_attention_fwd_planned",
     "sma_attention_fwd_static_workspace",
@@ -98,6 +99,8 @@ def _load() -> ctypes.CDLL:
                                   ctypes.c_void_p]
     lib.sma_attention_fwd.restype = ctypes.c_int
     lib.sma_attention_fwd.argtypes = [ctypes.POINTER(AttentionParams), ctypes.c_void_p]
+    lib.sma_sparse_attention_fwd.restype = ctypes.c_int
+    lib.sma_sparse_attention_fwd.argtypes = [ctypes.POINTER(AttentionParams), ctypes.c_void_p, ctypes.c_void_p]
     lib.sma_attention_workspace_bytes.restype = ctypes.c_size_t
     lib.sma_attention_workspace_bytes.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]
     lib.sma_attention_fwd_planned.restype = ctypes.c_int
@@ -133,6 +136,11 @@ def pack_mask(mask_ptr: int, packed_ptr: int, B: int, H: int, N: int, stream: in
 
 def attention_fwd(params: AttentionParams, stream: int) -> None:
     check(lib.sma_attention_fwd(ctypes.byref(params), stream))
+
+
+def sparse_attention_fwd(params: AttentionParams, mask_ptr: int, stream: int) -> None:
+    """pack_mask into params.mask_packed, then the forward pass, behind one call into the library."""
+    check(lib.sma_sparse_attention_fwd(ctypes.byref(params), mask_ptr, stream))
 
 
 def attention_workspace_bytes(B: int, H: int, N: int) -> int:

@@ -353,6 +353,13 @@ static size_t attention_workspace_bytes(int32_t B, int32_t H, int32_t N) {
 
 int sma_attention_fwd(const sma_attention_params* p, void* stream_v) { return attention_forward(p, nullptr, stream_v); }
 
+int sma_sparse_attention_fwd(const sma_attention_params* p, const uint8_t* mask, void* stream_v) {
+    if (!p || !mask) return SMA_ERR_NULL_POINTER;
+    if (!p->mask_packed) return SMA_ERR_NULL_POINTER;
+    if (int st = sma_pack_mask(mask, const_cast<uint32_t*>(p->mask_packed), p->B, p->H, p->N, stream_v)) return st;
+    return attention_forward(p, nullptr, stream_v);
+}
+
 size_t sma_attention_workspace_bytes(int32_t B, int32_t H, int32_t N) { return attention_workspace_bytes(B, H, N); }
 
 int sma_attention_fwd_planned(const sma_attention_params* p, void* workspace, size_t workspace_bytes, void* stream_v) {

@@ -94,15 +94,13 @@ def sparse_attention(q, k, v, mask):
 def sparse_attention_func(q, k, v, mask):
     """Inference-only variant of sparse_attention: no autograd graph, no log-sum-exp output."""
     _check_inputs(q, k, v, mask)
-    B, H, N, D = q.shape
-    scale = 1.0 / math.sqrt(D)
+    scale = 1.0 / math.sqrt(q.shape[-1])
     orig_dtype = q.dtype
     if orig_dtype == torch.float32:
         q, k, v = q.bfloat16(), k.bfloat16(), v.bfloat16()
-    with torch.no_grad():
-        mask_packed = pack_mask(mask)
-        out = torch.empty_like(q, memory_format=torch.contiguous_format)
-        sparse_attn_cuda.forward(q, k, v, mask_packed, out, None, scale, False)
+    # (nothing below is seen by autograd: the output is allocated here and written by the library)
+    out = torch.empty_like(q, memory_format=torch.contiguous_format)
+    sparse_attn_cuda.pack_and_forward(q, k, v, mask, out, None, scale, False)
     if orig_dtype == torch.float32:
         out = out.float()
     return out

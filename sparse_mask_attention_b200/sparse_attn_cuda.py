@@ -81,39 +81,49 @@ def pack_mask(mask: torch.Tensor) -> torch.Tensor:
     return packed
 
 
-def forward(q, k, v, mask_packed, out, lse, scale, is_training) -> None:
-    """Fused masked attention forward; writes ``out`` (and ``lse`` when ``is_training``) in place."""
+def _params_for(q, k, v, out, lse, scale, is_training):
+    """Checks q/k/v/out/lse against one another (one pass) and fills the argument block; returns it with q, k, v
+    made contiguous (the caller keeps them alive until the launch has been issued)."""
     _require(q.is_cuda, "q must be CUDA tensor")
     _require(q.dim() == 4, "q must be 4D")
-    _require(q.dtype in _DTYPES, "Unsupported dtype, need BF16 or FP16")
+    dtype = _DTYPES.get(q.dtype)
+    _require(dtype is not None, "Unsupported dtype, need BF16 or FP16")
     B, H, N, D = q.shape
     _require(D == 64, "head dimension must be 64")
-    for name, t in (("k", k), ("v", v), ("out", out)):
-        _require(t.shape == q.shape, "%s must have the shape of q" % name)
-        _require(t.dtype == q.dtype, "%s must have the dtype of q" % name)
-        _require(t.device == q.device, "%s must be on the device of q" % name)
-    n_words = (N + 31) // 32
-    _require(mask_packed.device == q.device, "mask_packed must be on the device of q")
-    _require(mask_packed.dtype == torch.int32, "mask_packed must be int32")
-    _require(tuple(mask_packed.shape) == (B, H, N, n_words), "mask_packed must be [B, H, N, ceil(N/32)]")
+    sig = (q.shape, q.dtype, q.device)
+    if (k.shape, k.dtype, k.device) != sig or (v.shape, v.dtype, v.device) != sig or (out.shape, out.dtype, out.device) != sig:
+        for name, t in (("k", k), ("v", v), ("out", out)):
+            _require(t.shape == q.shape, "%s must have the shape of q" % name)
+            _require(t.dtype == q.dtype, "%s must have the dtype of q" % name)
+            _require(t.device == q.device, "%s must be on the device of q" % name)
     _require(out.is_contiguous(), "out must be contiguous")
     save_lse = bool(is_training)
     if save_lse:
         _require(lse is not None, "lse is required when is_training is true")
         _require(lse.device == q.device and lse.dtype == torch.float32, "lse must be float32 on the device of q")
         _require(tuple(lse.shape) == (B, H, N) and lse.is_contiguous(), "lse must be contiguous [B, H, N]")
-    q, k, v, mask_packed = q.contiguous(), k.contiguous(), v.contiguous(), mask_packed.contiguous()
-
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     params = _capi.AttentionParams()
     params.q, params.k, params.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
-    params.mask_packed = mask_packed.data_ptr()
     params.out = out.data_ptr()
     params.lse = lse.data_ptr() if save_lse else None
     params.B, params.H, params.N, params.D = B, H, N, D
     params.scale = float(scale)
-    params.dtype = _DTYPES[q.dtype]
+    params.dtype = dtype
     params.save_lse = int(save_lse)
     params.variant = int(variant)
+    return params, (q, k, v)
+
+
+def forward(q, k, v, mask_packed, out, lse, scale, is_training) -> None:
+    """Fused masked attention forward; writes ``out`` (and ``lse`` when ``is_training``) in place."""
+    params, keep = _params_for(q, k, v, out, lse, scale, is_training)
+    B, H, N = params.B, params.H, params.N
+    _require(mask_packed.device == q.device, "mask_packed must be on the device of q")
+    _require(mask_packed.dtype == torch.int32, "mask_packed must be int32")
+    _require(tuple(mask_packed.shape) == (B, H, N, (N + 31) // 32), "mask_packed must be [B, H, N, ceil(N/32)]")
+    mask_packed = mask_packed.contiguous()
+    params.mask_packed = mask_packed.data_ptr()
     with _device_guard(q.device):
         if N > PLAN_ABOVE_SEQ_LEN:
             nbytes = _capi.attention_workspace_bytes(B, H, N)
@@ -121,3 +131,27 @@ def forward(q, k, v, mask_packed, out, lse, scale, is_training) -> None:
             _capi.attention_fwd_planned(params, workspace.data_ptr(), nbytes, _stream_of(q.device))
         else:
             _capi.attention_fwd(params, _stream_of(q.device))
+
+
+def pack_and_forward(q, k, v, mask, out, lse, scale, is_training) -> torch.Tensor:
+    """``pack_mask(mask)`` followed by ``forward(...)`` with one call into the library (one trip through ctypes
+    instead of two); returns the packed mask.  Not part of the reference extension's interface: the Python layer
+    above uses it where the reference calls the two functions back to back (python/sparse_attention.py:139-146)."""
+    params, keep = _params_for(q, k, v, out, lse, scale, is_training)
+    B, H, N = params.B, params.H, params.N
+    _require(mask.device == q.device, "mask must be on the device of q")
+    _require(mask.dtype in (torch.bool, torch.uint8), "mask must be bool")
+    _require(tuple(mask.shape) == (B, H, N, N), "mask must be [B, H, N, N]")
+    mask = mask.contiguous()
+    packed = torch.empty((B, H, N, (N + 31) // 32), dtype=torch.int32, device=q.device)
+    params.mask_packed = packed.data_ptr()
+    with _device_guard(q.device):
+        if N > PLAN_ABOVE_SEQ_LEN:
+            stream = _stream_of(q.device)
+            _capi.pack_mask(mask.data_ptr(), packed.data_ptr(), B, H, N, stream)
+            nbytes = _capi.attention_workspace_bytes(B, H, N)
+            workspace = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+            _capi.attention_fwd_planned(params, workspace.data_ptr(), nbytes, stream)
+        else:
+            _capi.sparse_attention_fwd(params, mask.data_ptr(), _stream_of(q.device))
+    return packed

@@ -23,7 +23,9 @@ COMMON = ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step",
 
 
 def test_reference_arm_line():
-    d = _run_bench("--impl", "reference", "--steps", "1", "--warmup", "0")
+    d = _run_bench("--impl", "reference", "--steps", "2", "--warmup", "1")
+    assert d["steps"] == 2 and d["warmup"] == 1  # both honoured as given
+    assert set(d["config"]) == {"workload", "B_per_gpu", "H", "N", "D", "mask", "keep_prob", "step", "l2", "sharding"}
     for key in COMMON + ("impl",):
         assert key in d, key
     assert d["impl"] == "reference" and d["n_gpus"] == 1 and d["vs_baseline"] is None
@@ -38,13 +40,14 @@ def test_reference_arm_line():
 
 @pytest.mark.gpu
 def test_gpu_arm_line():
-    d = _run_bench("--steps", "3", "--warmup", "3", "--no-cpu-baseline")
+    d = _run_bench("--steps", "3", "--warmup", "3", "--repeats", "4", "--no-cpu-baseline", "--no-extras")
     for key in COMMON[:-1] + ("gpu_launches", "clocks", "roofline", "roofline_pack"):
         assert key in d, key
     assert "impl" not in d or d["impl"] != "reference"
     assert d["n_gpus"] == 1 and d["steps"] == 3 and d["scaling"] == "weak" and d["vs_baseline"] is None
     assert d["dtype"] == "f16" and d["data"] == "synthetic"
-    assert d["gpu_launches"] == 2 * d["steps"]  # one pack and one attention launch per step
+    assert d["repeats"] == 4 and len(d["timing"]["step_us_per_rank"]) == 1
+    assert d["gpu_launches"] == 2 * d["steps"] * d["repeats"]  # one pack and one attention launch per step
     assert d["value"] > 0 and d["ms_per_step"] > 0
     e2e = d["e2e"]
     assert e2e["value"] > 0 and e2e["unit"] == d["unit"]
@@ -55,7 +58,7 @@ def test_gpu_arm_line():
         r = d[name]
         assert r["bound"] == bound and r["unit"] == unit and r["peak"] > 0
         assert abs(r["frac"] - r["achieved"] / r["peak"]) < 1e-9
-        assert 0 < r["frac"] < 1.2 and r["traffic"] > 0
+        assert 0 < r["frac"] < 1.2 and r["traffic"] > 0 and r["traffic_source"].startswith("profiles/")
         b2b = r["back_to_back"]
         assert 0 < b2b["ms_per_launch"] and abs(b2b["frac"] - b2b["achieved"] / r["peak"]) < 1e-9
     clocks = d["clocks"]
