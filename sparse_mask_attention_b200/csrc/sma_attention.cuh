@@ -443,13 +443,48 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                         }
                         // The tile loop is one rolled body (mask + maximum, then exponentials + P) on one register
                         // set, one tile per pass: the loop lives at the edge of what instruction fetch sustains, and
-                        // every unrolled or software-pipelined form that was tried ran slower.
+                        // every unrolled form that was tried ran slower.  A warp issues in order, so an instruction
+                        // whose result the next one needs at once (a barrier test, the wait for a tensor-memory load or
+                        // store) costs its whole latency, and with the two warps of a scheduler taking turns a warp's own
+                        // chain is what a pass costs.  The loop therefore keeps such pairs apart: the barriers of the
+                        // next tile's S and of this warp's turn are tested at the top and looked at after the masking,
+                        // the next tile's scores are requested right after the exponentials, and the wait for the P
+                        // stores with the arrival on bar_p_full moves to the top of the next pass.
+                        uint32_t pub_bar = 0;  // bar_p_full of the tile whose P has been stored but not yet published
 #pragma unroll 1
                         for (int local = 0; local < count; ++local) {
                             const uint32_t s_col = kColS + 64u * sbuf;  // S of this tile; P goes over the same columns
+                            const uint32_t my_bar = a_bar_p_full + 8 * sbuf;
+                            uint32_t nbuf = sbuf + 1, nphase = sphase;  // S/P buffer and phase of the tile after this one
+                            if (nbuf == kSBuffers) {
+                                nbuf = 0;
+                                nphase ^= 1u;
+                            }
+                            const bool have_next = local + 1 < count;
+                            const uint32_t e_next = have_next ? lds_u16(a_entries + 2 * (local + 1)) : 0u;
+                            const uint32_t next_bar = a_bar_s_full + 8 * nbuf;
+                            // scores of the next tile into the score registers (S runs two tiles ahead: normally complete)
+                            auto request_next = [&](bool next_ready) {
+                                if (have_next) {
+                                    if (!next_ready) swait(next_bar, nphase);
+                                    tc_fence_after_sync();
+                                    if ((e_next >> (8 + wq)) & 1u) {
+                                        tmem_ld32_f32(tmem_lane + kColS + 64u * nbuf, &sc[0]);
+                                        tmem_ld32_f32(tmem_lane + kColS + 64u * nbuf + 32, &sc[32]);
+                                    }
+                                }
+                            };
                             if ((e_cur >> (8 + wq)) & 1u) {
                                 const uint2 w = lds_v2(a_row + ((e_cur & (kChunkTiles - 1)) << 3));
-                                tmem_wait_ld();  // scores of this tile (requested at the end of the previous step)
+                                const bool next_ready = have_next && mbar_test_wait_a(next_bar, nphase);
+                                [[maybe_unused]] bool turn_ready = false;
+                                if constexpr (kTurns) turn_ready = mbar_test_wait_a(a_my_turn, turns & 1u);
+                                tmem_wait_ld();  // scores of this tile (requested during the previous pass)
+                                if (pub_bar) {   // the previous tile's P stores have long landed
+                                    tmem_wait_st();
+                                    tc_fence_before_sync();
+                                    mbar_arrive_a(pub_bar);
+                                }
                                 float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
                                 for (int j = 0; j < 32; ++j) {
@@ -463,7 +498,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                                 const float alpha = advance_max(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), neg_mc);
                                 if constexpr (kTurns) {
                                     if (*other_alive) {
-                                        wait(a_my_turn, turns & 1u);
+                                        if (!turn_ready) wait(a_my_turn, turns & 1u);
                                         ++turns;
                                     }
                                 }
@@ -494,11 +529,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                                     }
                                     tmem_st16(tmem_lane + s_col + half * 16, pk);
                                     if constexpr (kSplitP) tmem_st16(tmem_lane + s_col + 32 + half * 16, pk_lo);
+                                    if constexpr (kTurns) {
+                                        // the other warp's turn, once half of this warp's exponentials are through: its
+                                        // first ones then run under the rest of these, and the hand-over costs nothing
+                                        // (handing over at the start, so that both run together, lost 12 %; at the end 1 %)
+                                        if (half == 0) {
+                                            __syncwarp();
+                                            if (lane == 0) mbar_arrive_a(a_other_turn);
+                                        }
+                                    }
                                 }
-                                if constexpr (kTurns) {
-                                    __syncwarp();
-                                    if (lane == 0) mbar_arrive_a(a_other_turn);  // the other warp's turn
-                                }
+                                request_next(next_ready);
                                 float l_even, l_odd;
                                 unpack_f32x2(add_f32x2(add_f32x2(ls2[0], ls2[1]), add_f32x2(ls2[2], ls2[3])), l_even, l_odd);
                                 l_run = fmaf(l_run, alpha, l_even + l_odd);
@@ -506,7 +547,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                                 // rescale the O accumulator when some row of this warp moved its reference max
                                 if (__any_sync(0xFFFFFFFFu, alpha != 1.f)) {
                                     // every P V issued so far must have landed in O: the newest one is tile g-1 (alpha != 1
-                                    // implies that an earlier tile of this item kept something, so g >= 1)
+                                    // implies that an earlier tile of this item kept something, so g >= 1), whose P was
+                                    // published at the top of this pass or when its chunk ended
                                     swait(a_bar_pv_done + 8 * ((g - 1) % kStages), ((g - 1) / kStages) & 1);
                                     tc_fence_after_sync();
                                     rescale_o_row(tmem_lane + kColO, alpha);
@@ -514,34 +556,31 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                             } else {
                                 // none of this warp's rows keeps a key of the tile: P = 0, nothing else changes; a turn at
                                 // the exponentials that this warp holds goes straight back
+                                if (pub_bar) {
+                                    tmem_wait_st();
+                                    tc_fence_before_sync();
+                                    mbar_arrive_a(pub_bar);
+                                }
                                 pass_turn_on();
                                 uint32_t z[32];
 #pragma unroll
                                 for (int j = 0; j < 32; ++j) z[j] = 0u;
                                 tmem_st32(tmem_lane + s_col, z);
                                 if constexpr (kSplitP) tmem_st32(tmem_lane + s_col + 32, z);
+                                request_next(false);
                             }
-                            tmem_wait_st();
-                            tc_fence_before_sync();
-                            mbar_arrive_a(a_bar_p_full + 8 * sbuf);
+                            pub_bar = my_bar;
                             if (fin_on) finish_pending();  // the previous item, behind this item's first tile
 
                             ++g;
-                            if (++sbuf == kSBuffers) {
-                                sbuf = 0;
-                                sphase ^= 1u;
-                            }
-                            // scores of the next tile into the registers that have just been used up
-                            if (local + 1 < count) {
-                                e_cur = lds_u16(a_entries + 2 * (local + 1));
-                                swait(a_bar_s_full + 8 * sbuf, sphase);
-                                tc_fence_after_sync();
-                                if ((e_cur >> (8 + wq)) & 1u) {
-                                    tmem_ld32_f32(tmem_lane + kColS + 64u * sbuf, &sc[0]);
-                                    tmem_ld32_f32(tmem_lane + kColS + 64u * sbuf + 32, &sc[32]);
-                                }
-                            }
+                            sbuf = nbuf;
+                            sphase = nphase;
+                            e_cur = e_next;
                         }
+                        // the chunk's last tile is published here
+                        tmem_wait_st();
+                        tc_fence_before_sync();
+                        mbar_arrive_a(pub_bar);
                     }
                     mbar_arrive_a(a_bar_slot_free + 8 * slot);  // this thread is done with the chunk
                     ++u;
