@@ -17,18 +17,9 @@
 
 namespace sma {
 
-#ifndef SMA_PACK_THREADS
-#define SMA_PACK_THREADS 256
-#endif
-#ifndef SMA_PACK_UNROLL
-#define SMA_PACK_UNROLL 1
-#endif
-#ifndef SMA_PACK_BLOCKS_PER_SM
-#define SMA_PACK_BLOCKS_PER_SM 8
-#endif
-constexpr int kPackThreads = SMA_PACK_THREADS;
-constexpr int kPackUnroll = SMA_PACK_UNROLL;  // independent 32-byte loads in flight per thread
-constexpr int kPackBlocksPerSM = SMA_PACK_BLOCKS_PER_SM;
+constexpr int kPackThreads = 256;
+constexpr int kPackUnroll = 1;       // independent 32-byte loads in flight per thread
+constexpr int kPackBlocksPerSM = 8;
 
 // Four mask bytes -> four bits (bit i = byte i != 0).
 __device__ __forceinline__ uint32_t bytes_to_nibble(uint32_t x) {
