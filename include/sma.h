@@ -20,7 +20,7 @@
 extern "C" {
 #endif
 
-#define SMA_ABI_VERSION 1
+#define SMA_ABI_VERSION 2
 
 typedef enum sma_status {
     SMA_OK                 = 0,
@@ -120,8 +120,34 @@ int sma_attention_fwd(const sma_attention_params* params, void* stream);
  * foreign-function layer per step, which for a headline-sized batch costs as much host time as the kernels run.
  * Replaces: the pair pack_mask() + forward() that the reference's Python layer issues for every call of
  * sparse_attention() (python/sparse_attention.py:139-146, 64 and 170-171; csrc/binding.cpp:9-66).
+ * tile_bits: NULL, or a device buffer of sma_tile_bits_bytes(B, H, N) bytes; with it the two kernels work as
+ * sma_pack_mask_tiles and sma_attention_fwd_tiles do (below).  A buffer given for a shape that has no side-band
+ * (sma_tile_bits_bytes() == 0, or a mask that is not 32-byte aligned) is ignored.
  */
-int sma_sparse_attention_fwd(const sma_attention_params* params, const uint8_t* mask, void* stream);
+int sma_sparse_attention_fwd(const sma_attention_params* params, const uint8_t* mask, void* tile_bits, void* stream);
+
+/*
+ * Packing that also tells the attention kernel where the mask keeps anything.
+ * The attention kernel visits only the 64-key tiles in which some query row of a 128-row block keeps a key; with
+ * sma_attention_fwd its loader warps find them by reading the packed words again, one warp per block.  The packing
+ * kernel already holds every packed word in a register, so here each of its warps also writes one 16-bit word of
+ * occupancy for the 32 packed words it produces: bit b = packed words 2b and 2b+1 of the 32 (the 64 keys of one tile
+ * in one mask row) hold a set bit.  tile_bits[i] covers packed words 32i..32i+31 of the flat [B, H, N, N/32] array;
+ * the buffer has sma_tile_bits_bytes(B, H, N) bytes, 1/64 of the packed mask.  sma_attention_fwd_tiles derives its
+ * tile lists from it (a few hundred bytes per block of query rows instead of the block's packed rows), loads the
+ * packed words only of chunks of 512 keys that hold a tile, and so also serves long, sparse sequences without the
+ * tile-list kernel and workspace of sma_attention_fwd_planned.
+ * Exists for N a multiple of 64 (sma_tile_bits_bytes() returns 0 otherwise: SMA_ERR_BAD_SHAPE), a mask that is
+ * 32-byte aligned and a tile_bits buffer that is 16-byte aligned (SMA_ERR_MISALIGNED otherwise).  `tile_bits` must describe `params->mask_packed` as it is when the
+ * attention kernel runs: a caller who edits the packed words afterwards uses sma_attention_fwd.
+ * Results are those of sma_pack_mask and sma_attention_fwd, bit for bit.
+ * No counterpart in the reference, whose kernel tests every tile of every row block for emptiness itself
+ * (csrc/sparse_attention.cu:236-252); the packed words are the reference's (csrc/sparse_attention.cu:549-568).
+ */
+size_t sma_tile_bits_bytes(int32_t B, int32_t H, int32_t N);
+int sma_pack_mask_tiles(const uint8_t* mask, uint32_t* packed, void* tile_bits, int32_t B, int32_t H, int32_t N,
+                        void* stream);
+int sma_attention_fwd_tiles(const sma_attention_params* params, const void* tile_bits, void* stream);
 
 /*
  * The same forward pass for long, sparse sequences, with a workspace.

@@ -11,7 +11,7 @@ import os
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG_DIR, "libsma_b200.so")
 
-SMA_ABI_VERSION = 1
+SMA_ABI_VERSION = 2
 SMA_DTYPE_F16 = 0
 SMA_DTYPE_BF16 = 1
 SMA_VARIANT_DEFAULT = 0
@@ -42,6 +42,9 @@ EXPORTED_SYMBOLS = (
     "sma_pack_mask",
     "sma_attention_fwd",
     "sma_sparse_attention_fwd",
+    "sma_tile_bits_bytes",
+    "sma_pack_mask_tiles",
+    "sma_attention_fwd_tiles",
     "sma_attention_workspace_bytes",
     "sma_attention_fwd_planned",
     "sma_attention_fwd_static_workspace",
@@ -100,7 +103,15 @@ def _load() -> ctypes.CDLL:
     lib.sma_attention_fwd.restype = ctypes.c_int
     lib.sma_attention_fwd.argtypes = [ctypes.POINTER(AttentionParams), ctypes.c_void_p]
     lib.sma_sparse_attention_fwd.restype = ctypes.c_int
-    lib.sma_sparse_attention_fwd.argtypes = [ctypes.POINTER(AttentionParams), ctypes.c_void_p, ctypes.c_void_p]
+    lib.sma_sparse_attention_fwd.argtypes = [ctypes.POINTER(AttentionParams), ctypes.c_void_p, ctypes.c_void_p,
+                                             ctypes.c_void_p]
+    lib.sma_tile_bits_bytes.restype = ctypes.c_size_t
+    lib.sma_tile_bits_bytes.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]
+    lib.sma_pack_mask_tiles.restype = ctypes.c_int
+    lib.sma_pack_mask_tiles.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32,
+                                        ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p]
+    lib.sma_attention_fwd_tiles.restype = ctypes.c_int
+    lib.sma_attention_fwd_tiles.argtypes = [ctypes.POINTER(AttentionParams), ctypes.c_void_p, ctypes.c_void_p]
     lib.sma_attention_workspace_bytes.restype = ctypes.c_size_t
     lib.sma_attention_workspace_bytes.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]
     lib.sma_attention_fwd_planned.restype = ctypes.c_int
@@ -138,9 +149,24 @@ def attention_fwd(params: AttentionParams, stream: int) -> None:
     check(lib.sma_attention_fwd(ctypes.byref(params), stream))
 
 
-def sparse_attention_fwd(params: AttentionParams, mask_ptr: int, stream: int) -> None:
-    """pack_mask into params.mask_packed, then the forward pass, behind one call into the library."""
-    check(lib.sma_sparse_attention_fwd(ctypes.byref(params), mask_ptr, stream))
+def sparse_attention_fwd(params: AttentionParams, mask_ptr: int, tile_bits_ptr, stream: int) -> None:
+    """pack_mask into params.mask_packed, then the forward pass, behind one call into the library.
+
+    tile_bits_ptr: None, or a device buffer of tile_bits_bytes(B, H, N) bytes for the occupancy side-band."""
+    check(lib.sma_sparse_attention_fwd(ctypes.byref(params), mask_ptr, tile_bits_ptr, stream))
+
+
+def tile_bits_bytes(B: int, H: int, N: int) -> int:
+    """Bytes of the occupancy side-band of a B x H x N mask; 0 when the shape has none (N % 64 != 0)."""
+    return int(lib.sma_tile_bits_bytes(B, H, N))
+
+
+def pack_mask_tiles(mask_ptr: int, packed_ptr: int, tile_bits_ptr: int, B: int, H: int, N: int, stream: int) -> None:
+    check(lib.sma_pack_mask_tiles(mask_ptr, packed_ptr, tile_bits_ptr, B, H, N, stream))
+
+
+def attention_fwd_tiles(params: AttentionParams, tile_bits_ptr: int, stream: int) -> None:
+    check(lib.sma_attention_fwd_tiles(ctypes.byref(params), tile_bits_ptr, stream))
 
 
 def attention_workspace_bytes(B: int, H: int, N: int) -> int:

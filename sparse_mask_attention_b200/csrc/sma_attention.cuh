@@ -12,7 +12,7 @@
 // for those rows.  Warp roles:
 //   * loader warp (1 per stream): per chunk it brings the 128 x 16-word strip of packed-mask words into
 //     shared memory (one TMA tile copy; plain loads for shapes a tensor map cannot describe), finds the
-//     non-empty tiles in it (or copies them from a list computed ahead, kPlanned) and publishes a chunk
+//     non-empty tiles in it (or takes them from a list or from occupancy bits computed ahead, kLists) and publishes a chunk
 //     descriptor; then it issues the TMA loads (128-byte swizzle) of the item's Q tile and of the listed
 //     K/V tile pairs into a three-stage ring, as the P V products release the stages.
 //   * MMA warp (1 per stream): one thread walks the stream's tile sequence, across chunks and work items
@@ -189,6 +189,10 @@ struct AttnArgs {
     const uint32_t* mask_packed;
     const uint32_t* plan;   // tile lists computed ahead (sma_plan.cuh), or nullptr: the loader warps build them
     uint32_t plan_stride;   // words per work item in plan
+    // Where the mask keeps anything, as written by the packing kernel next to the packed words (sma_pack.cuh): one
+    // 16-bit word per 32 consecutive packed words, bit b = words 2b, 2b+1 of them hold a set bit.  When given (N a
+    // multiple of 64, kListsFromBits kernel) the loader warps derive the tile lists from it.
+    const uint16_t* tile_bits;
     float* lse;
     int32_t BH;
     int32_t N;
@@ -204,8 +208,11 @@ struct AttnArgs {
 //           fp16 P cannot be multiplied with a bf16 V.
 // kSplitP : bf16 only.  true = P = hi + lo, both bf16, two P*V products per tile (16 significant bits, so
 //           the result meets the same tolerance as the fp16 path); false = P rounded once to bf16.
-// kPlanned: the tile lists come from AttnArgs::plan instead of being built by the loader warps.
-template <bool kBf16, bool kSplitP, bool kPlanned>
+// kLists  : where the loader warps take the tile lists from.  kListsFromStrips: they scan every chunk's mask strip.
+//           kListsFromPlan: AttnArgs::plan.  kListsFromBits: AttnArgs::tile_bits.  In the last two, strips of chunks
+//           without a tile are not loaded at all.  (One instantiation each: the kernel is sensitive to its code size.)
+constexpr int kListsFromStrips = 0, kListsFromPlan = 1, kListsFromBits = 2;
+template <bool kBf16, bool kSplitP, int kLists>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o,
@@ -856,7 +863,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                     const uint32_t a_entries = a_desc0 + slot * 32u + 8;
                     for (uint32_t i = 0; i < count && ok; ++i) {
                         const int t = static_cast<int>(__shfl_sync(0xFFFFFFFFu, lds_u16(a_entries + 2 * i), 0) & 0xFFu);
-                        if (!kPlanned && mask_tma && have_n && !pre) {
+                        if (kLists == kListsFromStrips && mask_tma && have_n && !pre) {
                             const uint32_t un = u + 1;
                             if (un < kSlots ||
                                 __all_sync(0xFFFFFFFFu, mbar_test_wait_a(a_bar_slot_free + 8 * (un & 1u), ((un >> 1) - 1) & 1u))) {
@@ -905,14 +912,69 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                     const long long it = static_cast<long long>(blockIdx.x) + static_cast<long long>(k) * gridDim.x;
                     return it < total_items ? static_cast<int>(it) : -1;
                 };
+                // Side-band bits of chunks c0..c0+3 of a work item, as this lane sees them: lane l looks at rows l, 32+l,
+                // 64+l, 96+l of the item; raw[g] byte cc = tile bits of chunk c0+cc in row 32g+l.  Only issues the loads.
+                auto load_bits = [&](int item, int c0, uint32_t (&raw)[4]) {
+                    const int bh = item_bh(item), row0 = item_row0(item);
+                    const size_t row_words0 = (static_cast<size_t>(bh) * N + row0) * nw;
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) raw[g] = 0u;
+#pragma unroll
+                    for (int cc = 0; cc < 4; ++cc) {
+                        const int c = c0 + cc;
+                        const int need = min(kChunkWords, nw - c * kChunkWords);  // words of the chunk in a row
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            if (c < num_chunks && row0 + 32 * g + lane < N) {
+                                const size_t widx = row_words0 + static_cast<size_t>(32 * g + lane) * nw + c * kChunkWords;
+                                const uint32_t in_block = static_cast<uint32_t>(widx) & 31u;
+                                uint32_t v = ldg_u16(args.tile_bits + (widx >> 5));
+                                // the chunk's words may run into the next block of 32
+                                if (in_block + need > 32u) v |= static_cast<uint32_t>(ldg_u16(args.tile_bits + (widx >> 5) + 1)) << 16;
+                                raw[g] |= ((v >> (in_block >> 1)) & ((1u << ((need + 1) >> 1)) - 1u)) << (8 * cc);
+                            }
+                        }
+                    }
+                };
+                // The same bits when every row has a whole number of chunks (N a multiple of 512): a row's bits are then
+                // one byte per chunk, the item's 128 rows are contiguous, and lane l takes rows 4l..4l+3.  Returns byte
+                // cc = tile bits of chunk c0+cc OR-ed over those four rows.  Covers one or two chunks per row and multiples
+                // of four (aligned 32-bit loads); other lengths use load_bits.
+                const bool row_bytes = (nw % kChunkWords) == 0 && (num_chunks <= 2 || (num_chunks & 3) == 0);
+                auto lane_bits = [&](int item, int c0) -> uint32_t {
+                    const uint8_t* base = reinterpret_cast<const uint8_t*>(args.tile_bits) +
+                                          (static_cast<size_t>(item_bh(item)) * N + item_row0(item) + 4 * lane) * num_chunks + c0;
+                    if (num_chunks == 1) {
+                        uint32_t x = ldg_u32(reinterpret_cast<const uint32_t*>(base));
+                        x |= x >> 16;
+                        return (x | (x >> 8)) & 0xFFu;
+                    }
+                    if (num_chunks == 2) {
+                        const uint32_t x = ldg_u32(reinterpret_cast<const uint32_t*>(base)) | ldg_u32(reinterpret_cast<const uint32_t*>(base + 4));
+                        return (x | (x >> 16)) & 0xFFFFu;
+                    }
+                    return ldg_u32(reinterpret_cast<const uint32_t*>(base)) | ldg_u32(reinterpret_cast<const uint32_t*>(base + num_chunks)) |
+                           ldg_u32(reinterpret_cast<const uint32_t*>(base + 2 * num_chunks)) |
+                           ldg_u32(reinterpret_cast<const uint32_t*>(base + 3 * num_chunks));
+                };
+                constexpr bool from_bits = kLists == kListsFromBits;
                 int item_next = take_item();
+                uint32_t mine_next = 0u;  // lane_bits of the first four chunks of item_next, requested an item ahead
+                if (from_bits && row_bytes && item_next >= 0) mine_next = lane_bits(item_next, 0);
                 while (item_next >= 0 && ok) {
                     const int item = item_next;
                     item_next = take_item();  // taken one item ahead: its first mask strip is requested early
                     const int bh = item_bh(item);
                     // Q tile into buffer r % 2, last used by item r-2: all its S products must be complete
                     if (r >= 2) wait(a_bar_q_free + 8 * (r & 1u), ((r >> 1) - 1) & 1u);
-                    if (leader && ok) {
+#ifdef SMA_WAIT_TEST_BUILD
+                    // test build only: on request, the first Q tile of stream 0 of CTA 0 is never asked for, nothing
+                    // completes its barrier, and this warp's wait for it runs out
+                    const bool withheld = g_test_withhold_q_load != 0 && blockIdx.x == 0 && stream == 0 && r == 0;
+#else
+                    constexpr bool withheld = false;
+#endif
+                    if (leader && ok && !withheld) {
                         const uint32_t bar = a_bar_q + 8 * (r & 1u);
                         mbar_arrive_expect_tx_a(bar, kQTileBytes);
                         tma_load_3d_a(q_a0 + (r & 1u) * kQTileBytes, &tmap_q, bar, 0, item_row0(item), bh);
@@ -920,7 +982,66 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                     __syncwarp();
                     pend_first_of_item = true;
                     bool item_has_tiles = false, last_marked = false;
-                    if constexpr (kPlanned) {
+                    if constexpr (from_bits) {
+                        // The packing kernel left one bit per (mask row, 64-key tile); OR-ed over the rows of each of the
+                        // item's four row groups they are its tile lists.  Chunks without a tile are passed over; when the
+                        // item's final chunk is one of those, an empty descriptor closes the item.
+                        uint32_t mine = mine_next;
+                        if (row_bytes && item_next >= 0) mine_next = lane_bits(item_next, 0);
+                        for (int c0 = 0; c0 < num_chunks && ok; c0 += 4) {
+                            uint32_t raw[4];  // per row group: byte cc = tile bits of chunk c0 + cc
+                            if (row_bytes) {
+                                if (c0 > 0) mine = lane_bits(item, c0);
+                                // rows 32g..32g+31 sit in lanes 8g..8g+7
+                                const uint32_t red = __reduce_or_sync(0xFFu << (lane & 24), mine);
+#pragma unroll
+                                for (int g = 0; g < 4; ++g) raw[g] = __shfl_sync(0xFFFFFFFFu, red, 8 * g);
+                            } else {
+                                load_bits(item, c0, raw);
+                                try_issue_s();
+#pragma unroll
+                                for (int g = 0; g < 4; ++g) raw[g] = __reduce_or_sync(0xFFFFFFFFu, raw[g]);
+                            }
+#pragma unroll 1
+                            for (int cc = 0; cc < 4 && c0 + cc < num_chunks && ok; ++cc) {
+                                const int c = c0 + cc;
+                                const uint32_t g0 = (raw[0] >> (8 * cc)) & 0xFFu, g1 = (raw[1] >> (8 * cc)) & 0xFFu,
+                                               g2 = (raw[2] >> (8 * cc)) & 0xFFu, g3 = (raw[3] >> (8 * cc)) & 0xFFu;
+                                const uint32_t any = g0 | g1 | g2 | g3;
+                                if (any == 0u) continue;
+                                const uint32_t slot = u & 1u;
+                                wait_slot_free(u);
+                                if (mask_tma) strip_tma(slot, item, c);
+                                if (lane < kChunkTiles && ((any >> lane) & 1u)) {
+                                    const uint32_t pos = __popc(any & ((1u << lane) - 1u));
+                                    const uint32_t flags = ((g0 >> lane) & 1u) | (((g1 >> lane) & 1u) << 1) |
+                                                           (((g2 >> lane) & 1u) << 2) | (((g3 >> lane) & 1u) << 3);
+                                    sts_u16(a_desc0 + slot * 32u + 8 + 2 * pos, (c * kChunkTiles + lane) | (flags << 8));
+                                }
+                                if (!mask_tma) {
+                                    strip_copy(slot, item, c);
+                                    if (leader) mbar_arrive_a(a_bar_strip_full + 8 * slot);
+                                }
+                                __syncwarp();
+                                const bool last = c + 1 == num_chunks;
+                                publish(slot, item, __popc(any), last);
+                                // (requesting the next descriptor's strip from inside the K loop, as the strip-scanning
+                                // loader does, was measured here too and gained nothing)
+                                issue_kv(slot, __popc(any), last, bh, false, 0, 0);
+                                item_has_tiles = true;
+                                last_marked = last;
+                                ++u;
+                            }
+                        }
+                        if (ok && !last_marked) {
+                            const uint32_t slot = u & 1u;
+                            wait_slot_free(u);
+                            if (leader) mbar_arrive_a(a_bar_strip_full + 8 * slot);  // no strip: keep the barrier's phase in step
+                            __syncwarp();
+                            publish(slot, item, 0u, true);
+                            ++u;
+                        }
+                    } else if constexpr (kLists == kListsFromPlan) {
                         // the item's list was computed ahead: count word, then 16-bit entries in ascending tile order;
                         // one chunk descriptor per chunk that holds tiles (one empty descriptor for an empty item)
                         const uint32_t* plan = args.plan + static_cast<size_t>(item) * args.plan_stride;

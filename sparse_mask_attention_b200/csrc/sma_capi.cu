@@ -31,7 +31,7 @@ struct DeviceInfo {
     bool checked = false;
     bool is_sm100 = false;
     int sm_count = 0;
-    bool attn_attr_set[8] = {false, false, false, false, false, false, false, false};
+    bool attn_attr_set[12] = {};
 };
 DeviceInfo g_dev[kMaxDevices];
 std::mutex g_dev_mutex;
@@ -180,10 +180,10 @@ cudaError_t launch_overlapped(void (*kernel)(KArgs...), unsigned blocks, unsigne
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...);
 }
 
-template <bool kBf16, bool kSplitP, bool kPlanned>
+template <bool kBf16, bool kSplitP, int kLists>
 int launch_attention(DeviceInfo* dev, int slot, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                      const CUtensorMap& to, const CUtensorMap& tm, const sma::AttnArgs& args, cudaStream_t stream) {
-    auto kernel = sma::attn_fwd_kernel<kBf16, kSplitP, kPlanned>;
+    auto kernel = sma::attn_fwd_kernel<kBf16, kSplitP, kLists>;
     constexpr size_t smem = sma::attn_smem_bytes();
     // One CTA per SM: the kernel allocates all 512 tensor-memory columns, and more than half of the
     // SM's shared memory keeps a second CTA from becoming resident next to it.
@@ -234,28 +234,43 @@ const char* sma_strerror(int status) {
 
 int sma_last_cuda_error(void) { return tls_cuda_error; }
 
-int sma_pack_mask(const uint8_t* mask, uint32_t* packed, int32_t B, int32_t H, int32_t N, void* stream_v) {
+// Bytes of the occupancy side-band for B x H x N, or 0 when the shape has none (N not a multiple of 64).
+static size_t tile_bits_bytes(int32_t B, int32_t H, int32_t N) {
+    if (B < 1 || H < 1 || N < 1 || N > SMA_MAX_SEQ_LEN || N % 64 != 0) return 0;
+    return static_cast<size_t>(1ull * B * H * N * (N / 32) / 32 * sizeof(uint16_t));
+}
+
+// Shared body of the packing entry points; tile_bits == nullptr: packed words only.
+static int pack_mask(const uint8_t* mask, uint32_t* packed, uint16_t* tile_bits, int32_t B, int32_t H, int32_t N,
+                     void* stream_v) {
     if (!mask || !packed) return SMA_ERR_NULL_POINTER;
     if (B < 1 || H < 1 || N < 1) return SMA_ERR_BAD_SHAPE;
     const unsigned long long rows = 1ull * B * H * N;
     if (rows > (1ull << 40) / static_cast<unsigned long long>(N)) return SMA_ERR_BAD_SHAPE;
     if (reinterpret_cast<uintptr_t>(packed) & 3u) return SMA_ERR_MISALIGNED;
+    const bool flat = (N % 32 == 0) && ((reinterpret_cast<uintptr_t>(mask) & 31u) == 0);
+    if (tile_bits) {
+        if (tile_bits_bytes(B, H, N) == 0) return SMA_ERR_BAD_SHAPE;
+        if (!flat || (reinterpret_cast<uintptr_t>(tile_bits) & 15u)) return SMA_ERR_MISALIGNED;
+    }
     DeviceInfo* dev = nullptr;
     if (int st = current_device_info(&dev)) return st;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
 
-    const bool flat = (N % 32 == 0) && ((reinterpret_cast<uintptr_t>(mask) & 31u) == 0);
     if (flat) {
         const size_t n_words = static_cast<size_t>(rows) * (N / 32);
-        const size_t per_block = static_cast<size_t>(sma::kPackThreads) * sma::kPackUnroll;
+        const size_t per_block = static_cast<size_t>(sma::kPackThreads) * sma::pack_unroll(tile_bits != nullptr);
         size_t blocks = (n_words + per_block - 1) / per_block;
         // One block per 256 words up to the grid limit (the kernel strides over the rest): blocks that finish
         // hand their SM to the next one, so SMs that become free early (the tail of a kernel running before this
         // one) take more of the work.  A grid capped at the resident blocks was 3 % slower alone and 2 % per step.
         if (blocks > 0x7FFFFFFFu) blocks = 0x7FFFFFFFu;
-        if (!cuda_ok(launch_overlapped(sma::pack_flat_kernel, static_cast<unsigned>(blocks), sma::kPackThreads, 0, stream,
-                                       mask, packed, n_words)))
-            return SMA_ERR_CUDA;
+        const cudaError_t e =
+            tile_bits ? launch_overlapped(sma::pack_flat_kernel<true>, static_cast<unsigned>(blocks), sma::kPackThreads, 0,
+                                          stream, mask, packed, tile_bits, n_words)
+                      : launch_overlapped(sma::pack_flat_kernel<false>, static_cast<unsigned>(blocks), sma::kPackThreads, 0,
+                                          stream, mask, packed, static_cast<uint16_t*>(nullptr), n_words);
+        if (!cuda_ok(e)) return SMA_ERR_CUDA;
     } else {
         const size_t warps_per_block = sma::kPackThreads / 32;
         size_t blocks = (static_cast<size_t>(rows) + warps_per_block - 1) / warps_per_block;
@@ -268,10 +283,23 @@ int sma_pack_mask(const uint8_t* mask, uint32_t* packed, int32_t B, int32_t H, i
     return cuda_ok(cudaGetLastError()) ? SMA_OK : SMA_ERR_CUDA;
 }
 
-// Shared body of the attention entry points.  plan == nullptr: the kernel's loader warps find the non-empty
-// tiles themselves; otherwise `plan` is a workspace of at least attention_workspace_bytes() bytes that the
-// tile-list kernel fills first.
-static int attention_forward(const sma_attention_params* p, uint32_t* plan, void* stream_v) {
+int sma_pack_mask(const uint8_t* mask, uint32_t* packed, int32_t B, int32_t H, int32_t N, void* stream_v) {
+    return pack_mask(mask, packed, nullptr, B, H, N, stream_v);
+}
+
+size_t sma_tile_bits_bytes(int32_t B, int32_t H, int32_t N) { return tile_bits_bytes(B, H, N); }
+
+int sma_pack_mask_tiles(const uint8_t* mask, uint32_t* packed, void* tile_bits, int32_t B, int32_t H, int32_t N,
+                        void* stream_v) {
+    if (!tile_bits) return SMA_ERR_NULL_POINTER;
+    return pack_mask(mask, packed, static_cast<uint16_t*>(tile_bits), B, H, N, stream_v);
+}
+
+// Shared body of the attention entry points.  plan == nullptr and tile_bits == nullptr: the kernel's loader warps
+// find the non-empty tiles themselves by reading the packed mask.  plan: a workspace of at least
+// attention_workspace_bytes() bytes that the tile-list kernel fills first.  tile_bits: the occupancy side-band that
+// sma_pack_mask_tiles wrote for this mask_packed.
+static int attention_forward(const sma_attention_params* p, uint32_t* plan, const uint16_t* tile_bits, void* stream_v) {
     if (!p) return SMA_ERR_NULL_POINTER;
     if (!p->q || !p->k || !p->v || !p->mask_packed || !p->out) return SMA_ERR_NULL_POINTER;
     if (p->save_lse && !p->lse) return SMA_ERR_NULL_POINTER;
@@ -288,6 +316,10 @@ static int attention_forward(const sma_attention_params* p, uint32_t* plan, void
     if (align16 & 15u) return SMA_ERR_MISALIGNED;
     if ((reinterpret_cast<uintptr_t>(p->mask_packed) & 3u) || (reinterpret_cast<uintptr_t>(p->lse) & 3u))
         return SMA_ERR_MISALIGNED;
+    if (tile_bits) {
+        if (tile_bits_bytes(p->B, p->H, p->N) == 0) return SMA_ERR_BAD_SHAPE;
+        if (reinterpret_cast<uintptr_t>(tile_bits) & 15u) return SMA_ERR_MISALIGNED;
+    }
 
     const bool bf16 = p->dtype == SMA_DTYPE_BF16;
     bool split_p = bf16;
@@ -319,6 +351,7 @@ static int attention_forward(const sma_attention_params* p, uint32_t* plan, void
     sma::AttnArgs args;
     args.mask_packed = p->mask_packed;
     args.plan = plan;
+    args.tile_bits = tile_bits;
     args.plan_stride = sma::plan_stride_words(p->N);
     args.lse = p->lse;
     args.BH = static_cast<int32_t>(BH);
@@ -329,18 +362,25 @@ static int attention_forward(const sma_attention_params* p, uint32_t* plan, void
     args.save_lse = p->save_lse ? 1 : 0;
     args.mask_tma = mask_tma ? 1 : 0;
 
-    if (plan) {
-        const unsigned items = static_cast<unsigned>(BH * num_q_tiles);
-        sma::build_tile_lists_kernel<<<items, sma::kPlanRows, 0, stream>>>(p->mask_packed, plan, static_cast<int>(BH),
-                                                                          p->N, num_q_tiles, args.plan_stride);
-        if (!cuda_ok(cudaGetLastError())) return SMA_ERR_CUDA;
-        if (!bf16) return launch_attention<false, false, true>(dev, 4, tq, tk, tv, to, tm, args, stream);
-        if (split_p) return launch_attention<true, true, true>(dev, 5, tq, tk, tv, to, tm, args, stream);
-        return launch_attention<true, false, true>(dev, 6, tq, tk, tv, to, tm, args, stream);
+    if (plan || tile_bits) {
+        if (plan) {
+            const unsigned items = static_cast<unsigned>(BH * num_q_tiles);
+            sma::build_tile_lists_kernel<<<items, sma::kPlanRows, 0, stream>>>(p->mask_packed, plan, static_cast<int>(BH),
+                                                                              p->N, num_q_tiles, args.plan_stride);
+            if (!cuda_ok(cudaGetLastError())) return SMA_ERR_CUDA;
+        }
+        if (plan) {
+            if (!bf16) return launch_attention<false, false, sma::kListsFromPlan>(dev, 4, tq, tk, tv, to, tm, args, stream);
+            if (split_p) return launch_attention<true, true, sma::kListsFromPlan>(dev, 5, tq, tk, tv, to, tm, args, stream);
+            return launch_attention<true, false, sma::kListsFromPlan>(dev, 6, tq, tk, tv, to, tm, args, stream);
+        }
+        if (!bf16) return launch_attention<false, false, sma::kListsFromBits>(dev, 8, tq, tk, tv, to, tm, args, stream);
+        if (split_p) return launch_attention<true, true, sma::kListsFromBits>(dev, 9, tq, tk, tv, to, tm, args, stream);
+        return launch_attention<true, false, sma::kListsFromBits>(dev, 10, tq, tk, tv, to, tm, args, stream);
     }
-    if (!bf16) return launch_attention<false, false, false>(dev, 0, tq, tk, tv, to, tm, args, stream);
-    if (split_p) return launch_attention<true, true, false>(dev, 1, tq, tk, tv, to, tm, args, stream);
-    return launch_attention<true, false, false>(dev, 2, tq, tk, tv, to, tm, args, stream);
+    if (!bf16) return launch_attention<false, false, sma::kListsFromStrips>(dev, 0, tq, tk, tv, to, tm, args, stream);
+    if (split_p) return launch_attention<true, true, sma::kListsFromStrips>(dev, 1, tq, tk, tv, to, tm, args, stream);
+    return launch_attention<true, false, sma::kListsFromStrips>(dev, 2, tq, tk, tv, to, tm, args, stream);
 }
 
 // Bytes of workspace for B x H x N, or 0 for a shape the attention entry points reject.
@@ -351,13 +391,24 @@ static size_t attention_workspace_bytes(int32_t B, int32_t H, int32_t N) {
     return static_cast<size_t>(items) * sma::plan_stride_words(N) * sizeof(uint32_t);
 }
 
-int sma_attention_fwd(const sma_attention_params* p, void* stream_v) { return attention_forward(p, nullptr, stream_v); }
+int sma_attention_fwd(const sma_attention_params* p, void* stream_v) {
+    return attention_forward(p, nullptr, nullptr, stream_v);
+}
 
-int sma_sparse_attention_fwd(const sma_attention_params* p, const uint8_t* mask, void* stream_v) {
+int sma_attention_fwd_tiles(const sma_attention_params* p, const void* tile_bits, void* stream_v) {
+    if (!tile_bits) return SMA_ERR_NULL_POINTER;
+    return attention_forward(p, nullptr, static_cast<const uint16_t*>(tile_bits), stream_v);
+}
+
+int sma_sparse_attention_fwd(const sma_attention_params* p, const uint8_t* mask, void* tile_bits, void* stream_v) {
     if (!p || !mask) return SMA_ERR_NULL_POINTER;
     if (!p->mask_packed) return SMA_ERR_NULL_POINTER;
-    if (int st = sma_pack_mask(mask, const_cast<uint32_t*>(p->mask_packed), p->B, p->H, p->N, stream_v)) return st;
-    return attention_forward(p, nullptr, stream_v);
+    // the side-band exists for N % 64 == 0 and a 32-byte aligned mask; the caller who passes a buffer for another
+    // shape gets the plain pair of kernels
+    uint16_t* bits = static_cast<uint16_t*>(tile_bits);
+    if (bits && (tile_bits_bytes(p->B, p->H, p->N) == 0 || (reinterpret_cast<uintptr_t>(mask) & 31u))) bits = nullptr;
+    if (int st = pack_mask(mask, const_cast<uint32_t*>(p->mask_packed), bits, p->B, p->H, p->N, stream_v)) return st;
+    return attention_forward(p, nullptr, bits, stream_v);
 }
 
 size_t sma_attention_workspace_bytes(int32_t B, int32_t H, int32_t N) { return attention_workspace_bytes(B, H, N); }
@@ -367,7 +418,7 @@ int sma_attention_fwd_planned(const sma_attention_params* p, void* workspace, si
     if (reinterpret_cast<uintptr_t>(workspace) & 15u) return SMA_ERR_MISALIGNED;
     const size_t need = attention_workspace_bytes(p->B, p->H, p->N);
     if (need != 0 && workspace_bytes < need) return SMA_ERR_WORKSPACE_TOO_SMALL;
-    return attention_forward(p, static_cast<uint32_t*>(workspace), stream_v);  // need == 0: the shape checks report it
+    return attention_forward(p, static_cast<uint32_t*>(workspace), nullptr, stream_v);  // need == 0: the shape checks report it
 }
 
 // ---- the entry point that allocates nothing -----------------------------------------------------------------
@@ -408,8 +459,16 @@ int sma_attention_fwd_static_workspace(const sma_attention_params* p, void* stre
     if (int st = static_workspace_of_current_device(&workspace)) return st;
     // Nothing in the workspace has to start at zero: the tile-list kernel writes every word the attention kernel
     // reads (the count of each work item and that many entries), so the previous call's leftovers are never seen.
-    return attention_forward(p, workspace, stream_v);  // need == 0: the shape checks in there report why
+    return attention_forward(p, workspace, nullptr, stream_v);  // need == 0: the shape checks in there report why
 }
+
+#ifdef SMA_WAIT_TEST_BUILD
+// Test build only (not declared in include/sma.h): while on, every attention launch leaves one Q tile unrequested.
+int sma_test_withhold_q_load(int on) {
+    const int value = on ? 1 : 0;
+    return cuda_ok(cudaMemcpyToSymbol(sma::g_test_withhold_q_load, &value, sizeof(int))) ? SMA_OK : SMA_ERR_CUDA;
+}
+#endif
 
 int sma_device_status(void) {
     if (!cuda_ok(cudaDeviceSynchronize())) return SMA_ERR_CUDA;

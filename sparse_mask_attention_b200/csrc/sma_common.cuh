@@ -116,7 +116,15 @@ __device__ __forceinline__ bool mbar_try_wait_suspend_a(uint32_t bar, uint32_t p
 // other waiter of the CTA gives up at its next poll instead of running out its own limit.  The limit is
 // kWaitLimitCycles of the SM clock (a second or two), not a poll count: a poll may return at once or sleep
 // for the whole hint.
+#ifdef SMA_WAIT_TEST_BUILD
+// Test build (libsma_b200_waittest.so, never the product library): waits give up after some ten milliseconds, and
+// the attention kernel can be told to leave one load unrequested, so that a test sees a wait run out and the
+// library report it.
+constexpr long long kWaitLimitCycles = 1ll << 24;
+__device__ int g_test_withhold_q_load = 0;
+#else
 constexpr long long kWaitLimitCycles = 1ll << 32;
+#endif
 constexpr uint32_t kSuspendHintNs = 20000;
 // The polling loop of a wait whose first test failed.  (Inlined: as an out-of-line call it needs the calling
 // convention's registers, which the softmax warps of the attention kernel, at their register cap, do not have.)

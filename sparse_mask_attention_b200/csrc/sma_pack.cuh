@@ -8,6 +8,8 @@
 // array and every thread turns one 32-byte vector load (ld.global.v8.b32, sm_100) into one output
 // word; a warp reads 1 KB and writes 128 B per step, both fully coalesced.  Other N take the row
 // path: one warp per mask row, one byte per lane, a warp ballot per output word.
+// On request the flat path also writes an occupancy side-band for the attention kernel (one bit per mask
+// row and 64-key tile), which no kernel of the reference has.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -18,7 +20,10 @@
 namespace sma {
 
 constexpr int kPackThreads = 256;
-constexpr int kPackUnroll = 1;       // independent 32-byte loads in flight per thread
+// independent 32-byte loads in flight per thread: one without the occupancy side-band (more were slower), two with
+// it, so that a warp's side-band store is a whole 32-bit word (a 16-bit store per 32 packed words cost 12 % of the
+// kernel's time, the 32-bit store per 64 costs 8 %)
+__host__ __device__ constexpr int pack_unroll(bool tiles) { return tiles ? 2 : 1; }
 constexpr int kPackBlocksPerSM = 8;
 
 // Four mask bytes -> four bits (bit i = byte i != 0).
@@ -42,26 +47,59 @@ __device__ __forceinline__ void ld_stream_256(const uint8_t* p, uint32_t (&r)[8]
                  : "l"(p));
 }
 
+// Even bits of x (bits 0, 2, 4, ...) gathered into the low 16 bits.
+__device__ __forceinline__ uint32_t even_bits(uint32_t x) {
+    x &= 0x55555555u;
+    x = (x | (x >> 1)) & 0x33333333u;
+    x = (x | (x >> 2)) & 0x0F0F0F0Fu;
+    x = (x | (x >> 4)) & 0x00FF00FFu;
+    return (x | (x >> 8)) & 0xFFFFu;
+}
+
 // Flat path.  Requires: mask 32-byte aligned, total bytes = 32 * n_words.  Launched with one block per
-// kPackThreads * kPackUnroll words (the grid stride only matters beyond the grid-size limit); kPackUnroll
-// independent 32-byte loads in flight per thread.
+// kPackThreads * pack_unroll words (the grid stride only matters beyond the grid-size limit); a warp takes
+// 32 * pack_unroll consecutive words.
+//
+// kTiles: the kernel also says where the mask keeps anything, for the attention kernel, which skips 64-key
+// tiles without a kept key and otherwise has to find them by reading the packed words again.  Per 32 consecutive
+// packed words there is one 16-bit word tile_bits[w / 32] whose bit b says that packed words 2b and 2b+1 of those 32
+// (64 keys of one mask row when N is a multiple of 64) hold a set bit.  Needs n_words to be a multiple of 64, which
+// holds for every N that is a multiple of 64, and tile_bits 4-byte aligned.
+template <bool kTiles>
 __global__ void __launch_bounds__(kPackThreads, kPackBlocksPerSM)
-pack_flat_kernel(const uint8_t* __restrict__ mask, uint32_t* __restrict__ packed, size_t n_words) {
+pack_flat_kernel(const uint8_t* __restrict__ mask, uint32_t* __restrict__ packed, uint16_t* __restrict__ tile_bits,
+                 size_t n_words) {
     grid_launch_dependents();
     grid_dependency_wait();  // the mask may be the previous kernel's output
-    const size_t block_words = static_cast<size_t>(kPackThreads) * kPackUnroll;
+    constexpr int kUnroll = pack_unroll(kTiles);
+    const size_t block_words = static_cast<size_t>(kPackThreads) * kUnroll;
     const size_t stride = static_cast<size_t>(gridDim.x) * block_words;
-    for (size_t base = static_cast<size_t>(blockIdx.x) * block_words + threadIdx.x; base < n_words; base += stride) {
-        uint32_t r[kPackUnroll][8];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (size_t base = static_cast<size_t>(blockIdx.x) * block_words + warp * (32 * kUnroll) + lane; base < n_words;
+         base += stride) {
+        uint32_t r[kUnroll][8];
 #pragma unroll
-        for (int u = 0; u < kPackUnroll; ++u) {
-            const size_t w = base + static_cast<size_t>(u) * kPackThreads;
+        for (int u = 0; u < kUnroll; ++u) {
+            const size_t w = base + 32 * u;
             if (w < n_words) ld_stream_256(mask + 32 * w, r[u]);
         }
+        uint32_t bits = 0;
 #pragma unroll
-        for (int u = 0; u < kPackUnroll; ++u) {
-            const size_t w = base + static_cast<size_t>(u) * kPackThreads;
-            if (w < n_words) packed[w] = pack32(r[u]);
+        for (int u = 0; u < kUnroll; ++u) {
+            const size_t w = base + 32 * u;
+            if (w < n_words) {
+                const uint32_t word = pack32(r[u]);
+                packed[w] = word;
+                if constexpr (kTiles) {
+                    // w - lane is a multiple of 32 and n_words is one too: the whole warp is here
+                    const uint32_t nz = __ballot_sync(0xFFFFFFFFu, word != 0u);
+                    bits |= even_bits(nz | (nz >> 1)) << (16 * u);
+                }
+            }
+        }
+        if constexpr (kTiles) {
+            // base - lane is a multiple of 64 and so is n_words: both halves of the 32-bit word are this warp's
+            if (lane == 0) *reinterpret_cast<uint32_t*>(tile_bits + (base >> 5)) = bits;
         }
     }
 }

@@ -48,7 +48,7 @@ build_tile_lists_kernel(const uint32_t* __restrict__ mask_packed, uint32_t* __re
     const int nw = (N + 31) >> 5;
     const int num_tiles = (N + kPlanTile - 1) / kPlanTile;
     const uint32_t tail_bits = (N & 31) ? ((1u << (N & 31)) - 1u) : 0xFFFFFFFFu;
-    const bool vector_rows = (nw & 3) == 0 && (reinterpret_cast<uintptr_t>(mask_packed) & 15u) == 0;
+    const bool vector_rows = (N & 127) == 0 && (reinterpret_cast<uintptr_t>(mask_packed) & 15u) == 0;
     uint32_t* out = plan + static_cast<size_t>(item) * stride_words;
     uint16_t* entries = reinterpret_cast<uint16_t*>(out + 1);
     constexpr int kMaxPlanTiles = 16384 / kPlanTile;

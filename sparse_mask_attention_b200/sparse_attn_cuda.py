@@ -146,12 +146,19 @@ def pack_and_forward(q, k, v, mask, out, lse, scale, is_training) -> torch.Tenso
     packed = torch.empty((B, H, N, (N + 31) // 32), dtype=torch.int32, device=q.device)
     params.mask_packed = packed.data_ptr()
     with _device_guard(q.device):
-        if N > PLAN_ABOVE_SEQ_LEN:
+        if N > PLAN_ABOVE_SEQ_LEN and N % 64 == 0 and mask.data_ptr() % 32 == 0:
+            # long sequences: the packing kernel leaves a bit per (mask row, 64-key tile) beside the packed words and
+            # the attention kernel takes its tile lists from them -- as fast as the tile-list kernel with its
+            # workspace (below), with two launches instead of three and one call into the library.  Up to
+            # PLAN_ABOVE_SEQ_LEN the attention kernel's own scan of the packed mask is faster than either.
+            tile_bits = torch.empty(_capi.tile_bits_bytes(B, H, N) // 2, dtype=torch.int16, device=q.device)
+            _capi.sparse_attention_fwd(params, mask.data_ptr(), tile_bits.data_ptr(), _stream_of(q.device))
+        elif N > PLAN_ABOVE_SEQ_LEN:
             stream = _stream_of(q.device)
             _capi.pack_mask(mask.data_ptr(), packed.data_ptr(), B, H, N, stream)
             nbytes = _capi.attention_workspace_bytes(B, H, N)
             workspace = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
             _capi.attention_fwd_planned(params, workspace.data_ptr(), nbytes, stream)
         else:
-            _capi.sparse_attention_fwd(params, mask.data_ptr(), _stream_of(q.device))
+            _capi.sparse_attention_fwd(params, mask.data_ptr(), None, _stream_of(q.device))
     return packed
