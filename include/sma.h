@@ -165,6 +165,23 @@ int sma_attention_fwd_planned(const sma_attention_params* params, void* workspac
                               void* stream);
 
 /*
+ * Backward pass: dq, dk, dv (same shape, layout and dtype as q, k, v) from dout, the upstream gradient of out.
+ * `params` is the forward call's (q, k, v, mask_packed, B, H, N, D = 64, scale, dtype) with out and lse holding
+ * what the forward pass wrote with save_lse = 1; the attention probabilities are recomputed from lse, and key
+ * blocks in which a block of query rows keeps nothing are skipped as in the forward pass.
+ * `workspace`: sma_attention_bwd_workspace_bytes(B, H, N) bytes of device memory, 16-byte aligned (the row sums
+ * dout . out and an fp32 accumulator for dq; contents on entry do not matter).  dq is summed by fp32 atomics over
+ * the key blocks, so its last bits can differ from run to run; dk and dv are deterministic.
+ * Replaces: sparse_attention_bwd_bf16(params, dout, dq, dk, dv, stream), csrc/sparse_attention.h:57-64, which the
+ * reference declares but never defines, and sparse_attn_cuda.backward(dout, q, k, v, out, lse, mask_packed, dq, dk,
+ * dv, scale), which its autograd function calls (python/sparse_attention.py:90-94) but its extension does not
+ * export; the gradient it computes is the one of the PyTorch branch there (python/sparse_attention.py:96-111).
+ */
+size_t sma_attention_bwd_workspace_bytes(int32_t B, int32_t H, int32_t N);
+int sma_attention_bwd(const sma_attention_params* params, const void* dout, void* dq, void* dk, void* dv,
+                      void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * sma_attention_fwd_planned without a workspace argument, for callers that must not allocate device memory and
  * have none to spare: code that runs after a service has frozen its memory budget, inside a latency-critical
  * loop where cudaMalloc's device-wide synchronisation is not acceptable, or behind a plug-in interface that

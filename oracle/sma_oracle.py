@@ -11,6 +11,7 @@ Reference code followed (paths inside xgbj/sparse-mask-attention):
   pack_mask_*      python/sparse_attention.py:184-201 (CPU branch), csrc/sparse_attention.cu:549-568
   attention_*      python/sparse_attention.py:24-42 (sparse_attention_ref), duplicate run.py:158-165
   lse              python/sparse_attention.py:72-74 (torch.logsumexp over the masked, scaled scores)
+  attention_bwd_np python/sparse_attention.py:96-111 (the autograd function's PyTorch gradient)
 """
 from __future__ import annotations
 
@@ -92,6 +93,37 @@ def attention_np(q, k, v, mask, scale=None, dtype=np.float32):
         lse = np.where(denom[..., 0] > 0, safe_max[..., 0] + np.log(denom[..., 0]), dtype(-np.inf))
     out = np.matmul(attn, v)
     return out.astype(dtype), lse.astype(dtype)
+
+
+def attention_bwd_np(q, k, v, mask, dout, scale=None, dtype=np.float64):
+    """dq, dk, dv of ``out = softmax(mask ? scale*q k^T : -inf) v`` for the upstream gradient ``dout``.
+
+    Restates the PyTorch fallback of the reference's autograd function (python/sparse_attention.py:96-111):
+    attn with rows that keep nothing set to 0, dv = attn^T dout, dattn = dout v^T (0 where masked),
+    ds = scale * attn * (dattn - rowsum(dattn * attn)), dq = ds k, dk = ds^T q.
+    """
+    q = np.asarray(q, dtype=dtype)
+    k = np.asarray(k, dtype=dtype)
+    v = np.asarray(v, dtype=dtype)
+    dout = np.asarray(dout, dtype=dtype)
+    mask = np.asarray(mask).astype(bool)
+    D = q.shape[-1]
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    scores = np.matmul(q, np.swapaxes(k, -1, -2)) * dtype(scale)
+    scores = np.where(mask, scores, dtype(-np.inf))
+    row_max = scores.max(axis=-1, keepdims=True)
+    safe_max = np.where(np.isfinite(row_max), row_max, dtype(0))
+    e = np.exp(scores - safe_max)
+    denom = e.sum(axis=-1, keepdims=True)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        attn = np.where(denom > 0, e / denom, dtype(0))
+    dv = np.matmul(np.swapaxes(attn, -1, -2), dout)
+    dattn = np.where(mask, np.matmul(dout, np.swapaxes(v, -1, -2)), dtype(0))
+    ds = attn * (dattn - (dattn * attn).sum(axis=-1, keepdims=True)) * dtype(scale)
+    dq = np.matmul(ds, k)
+    dk = np.matmul(np.swapaxes(ds, -1, -2), q)
+    return dq.astype(dtype), dk.astype(dtype), dv.astype(dtype)
 
 
 def attention_torch_cpu(q, k, v, mask):

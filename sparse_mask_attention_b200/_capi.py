@@ -48,6 +48,8 @@ EXPORTED_SYMBOLS = (
     "sma_attention_workspace_bytes",
     "sma_attention_fwd_planned",
     "sma_attention_fwd_static_workspace",
+    "sma_attention_bwd_workspace_bytes",
+    "sma_attention_bwd",
     "sma_device_status",
 )
 
@@ -119,6 +121,11 @@ def _load() -> ctypes.CDLL:
                                               ctypes.c_void_p]
     lib.sma_attention_fwd_static_workspace.restype = ctypes.c_int
     lib.sma_attention_fwd_static_workspace.argtypes = [ctypes.POINTER(AttentionParams), ctypes.c_void_p]
+    lib.sma_attention_bwd_workspace_bytes.restype = ctypes.c_size_t
+    lib.sma_attention_bwd_workspace_bytes.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]
+    lib.sma_attention_bwd.restype = ctypes.c_int
+    lib.sma_attention_bwd.argtypes = [ctypes.POINTER(AttentionParams)] + [ctypes.c_void_p] * 5 + [ctypes.c_size_t,
+                                                                                                 ctypes.c_void_p]
     lib.sma_device_status.restype = ctypes.c_int
     lib.sma_device_status.argtypes = []
     if lib.sma_abi_version() != SMA_ABI_VERSION:
@@ -175,6 +182,16 @@ def attention_workspace_bytes(B: int, H: int, N: int) -> int:
 
 def attention_fwd_planned(params: AttentionParams, workspace_ptr: int, workspace_bytes: int, stream: int) -> None:
     check(lib.sma_attention_fwd_planned(ctypes.byref(params), workspace_ptr, workspace_bytes, stream))
+
+
+def attention_bwd_workspace_bytes(B: int, H: int, N: int) -> int:
+    return int(lib.sma_attention_bwd_workspace_bytes(B, H, N))
+
+
+def attention_bwd(params: AttentionParams, dout_ptr: int, dq_ptr: int, dk_ptr: int, dv_ptr: int, workspace_ptr: int,
+                  workspace_bytes: int, stream: int) -> None:
+    check(lib.sma_attention_bwd(ctypes.byref(params), dout_ptr, dq_ptr, dk_ptr, dv_ptr, workspace_ptr, workspace_bytes,
+                                stream))
 
 
 def attention_fwd_static_workspace(params: AttentionParams, stream: int) -> None:

@@ -4,7 +4,6 @@
 #include "../../include/sma.h"
 
 #include <cmath>
-#include <cstdio>
 #include <cstring>
 #include <mutex>
 #include <utility>
@@ -13,6 +12,7 @@
 #include "sma_common.cuh"
 #include "sma_pack.cuh"
 #include "sma_plan.cuh"
+#include "sma_backward.cuh"
 
 namespace {
 
@@ -32,6 +32,7 @@ struct DeviceInfo {
     bool is_sm100 = false;
     int sm_count = 0;
     bool attn_attr_set[12] = {};
+    bool bwd_attr_set[2] = {};
 };
 DeviceInfo g_dev[kMaxDevices];
 std::mutex g_dev_mutex;
@@ -59,6 +60,14 @@ int current_device_info(DeviceInfo** out) {
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// Makes the device's primary context current to the calling host thread.  Runtime calls do that by themselves, the
+// driver call that encodes a tensor map does not: in a thread that has made no context-binding runtime call yet (a
+// framework's worker thread entering the library for the first time) it fails with CUDA_ERROR_INVALID_CONTEXT.
+bool bind_primary_context() {
+    int dev = 0;
+    return cudaGetDevice(&dev) == cudaSuccess && cudaSetDevice(dev) == cudaSuccess;
+}
 
 EncodeTiledFn encode_tiled_fn() {
     static EncodeTiledFn fn = []() -> EncodeTiledFn {
@@ -113,10 +122,13 @@ int make_qkv_tensor_map(CUtensorMap* map, const void* base, int BH, int N, int b
     const cuuint64_t strides[2] = {128, static_cast<cuuint64_t>(N) * 128};
     const cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_rows), 1};
     const cuuint32_t elem_strides[3] = {1, 1, 1};
-    const CUresult r = encode(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
-                              const_cast<void*>(base), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    auto encode_once = [&]() {
+        return encode(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                      const_cast<void*>(base), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    };
+    CUresult r = encode_once();
+    if (r == CUDA_ERROR_INVALID_CONTEXT && bind_primary_context()) r = encode_once();
     if (r != CUDA_SUCCESS) {
         tls_cuda_error = static_cast<int>(cudaErrorInvalidValue);
         return SMA_ERR_CUDA;
@@ -149,9 +161,13 @@ int make_mask_tensor_map(CUtensorMap* map, const uint32_t* base, int BH, int N) 
     const cuuint64_t strides[2] = {nw * 4, static_cast<cuuint64_t>(N) * nw * 4};
     const cuuint32_t box[3] = {sma::kChunkWords, sma::kBlockM, 1};
     const cuuint32_t elem_strides[3] = {1, 1, 1};
-    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<uint32_t*>(base), dims, strides, box,
-                              elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-                              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    auto encode_once = [&]() {
+        return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<uint32_t*>(base), dims, strides, box, elem_strides,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    };
+    CUresult r = encode_once();
+    if (r == CUDA_ERROR_INVALID_CONTEXT && bind_primary_context()) r = encode_once();
     if (r != CUDA_SUCCESS) {
         tls_cuda_error = static_cast<int>(cudaErrorInvalidValue);
         return SMA_ERR_CUDA;
@@ -180,6 +196,22 @@ cudaError_t launch_overlapped(void (*kernel)(KArgs...), unsigned blocks, unsigne
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...);
 }
 
+// An ordinary launch whose outcome is the launch call's own return value.  (The error state that cudaGetLastError
+// reads is per host thread and shared with everything else that thread runs: another library's harmless failed
+// query, left there, would be reported as this library's launch failure.)
+template <typename... KArgs, typename... Args>
+cudaError_t launch_plain(void (*kernel)(KArgs...), unsigned blocks, unsigned threads, size_t smem, cudaStream_t stream,
+                         Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(blocks);
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cfg.attrs = nullptr;
+    cfg.numAttrs = 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...);
+}
+
 template <bool kBf16, bool kSplitP, int kLists>
 int launch_attention(DeviceInfo* dev, int slot, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                      const CUtensorMap& to, const CUtensorMap& tm, const sma::AttnArgs& args, cudaStream_t stream) {
@@ -205,6 +237,46 @@ int launch_attention(DeviceInfo* dev, int slot, const CUtensorMap& tq, const CUt
 }
 
 }  // namespace
+
+template <bool kBf16>
+static int launch_backward(DeviceInfo* dev, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                           const CUtensorMap& tdo, const sma::BwdArgs& args, const void* dout, const void* out, void* dq,
+                           cudaStream_t stream) {
+    const size_t rows = static_cast<size_t>(args.BH) * args.N;
+    {
+        const size_t warps_per_block = 8;
+        size_t blocks = (rows + warps_per_block - 1) / warps_per_block;
+        const size_t cap = static_cast<size_t>(dev->sm_count) * 8;
+        if (blocks > cap) blocks = cap;
+        if (!cuda_ok(launch_plain(sma::bwd_prepare_kernel<kBf16>, static_cast<unsigned>(blocks), 256, 0, stream,
+                                  static_cast<const uint32_t*>(dout), static_cast<const uint32_t*>(out),
+                                  const_cast<float*>(args.delta), args.dq_accum, rows)))
+            return SMA_ERR_CUDA;
+    }
+    auto kernel = sma::attn_bwd_kernel<kBf16>;
+    constexpr size_t smem = sma::bwd_smem_bytes();
+    static_assert(smem > 116 * 1024 && smem <= 227 * 1024, "shared memory must pin occupancy to one CTA per SM");
+    {
+        std::lock_guard<std::mutex> lock(g_dev_mutex);
+        if (!dev->bwd_attr_set[kBf16 ? 1 : 0]) {
+            if (!cuda_ok(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem))))
+                return SMA_ERR_CUDA;
+            dev->bwd_attr_set[kBf16 ? 1 : 0] = true;
+        }
+    }
+    const unsigned blocks = static_cast<unsigned>(static_cast<long long>(args.BH) * ((args.N + sma::kBwdBlock - 1) / sma::kBwdBlock));
+    if (!cuda_ok(launch_plain(kernel, blocks, sma::kBwdThreads, smem, stream, tq, tk, tv, tdo, args))) return SMA_ERR_CUDA;
+    {
+        const size_t n2 = rows * sma::kBwdDim / 2;
+        size_t blocks2 = (n2 + 255) / 256;
+        const size_t cap = static_cast<size_t>(dev->sm_count) * 16;
+        if (blocks2 > cap) blocks2 = cap;
+        if (!cuda_ok(launch_plain(sma::bwd_finish_kernel<kBf16>, static_cast<unsigned>(blocks2), 256, 0, stream,
+                                  reinterpret_cast<const float2*>(args.dq_accum), static_cast<uint32_t*>(dq), n2)))
+            return SMA_ERR_CUDA;
+    }
+    return SMA_OK;
+}
 
 extern "C" {
 
@@ -280,7 +352,7 @@ static int pack_mask(const uint8_t* mask, uint32_t* packed, uint16_t* tile_bits,
                                        mask, packed, static_cast<size_t>(rows), N)))
             return SMA_ERR_CUDA;
     }
-    return cuda_ok(cudaGetLastError()) ? SMA_OK : SMA_ERR_CUDA;
+    return SMA_OK;
 }
 
 int sma_pack_mask(const uint8_t* mask, uint32_t* packed, int32_t B, int32_t H, int32_t N, void* stream_v) {
@@ -365,9 +437,9 @@ static int attention_forward(const sma_attention_params* p, uint32_t* plan, cons
     if (plan || tile_bits) {
         if (plan) {
             const unsigned items = static_cast<unsigned>(BH * num_q_tiles);
-            sma::build_tile_lists_kernel<<<items, sma::kPlanRows, 0, stream>>>(p->mask_packed, plan, static_cast<int>(BH),
-                                                                              p->N, num_q_tiles, args.plan_stride);
-            if (!cuda_ok(cudaGetLastError())) return SMA_ERR_CUDA;
+            if (!cuda_ok(launch_plain(sma::build_tile_lists_kernel, items, sma::kPlanRows, 0, stream, p->mask_packed, plan,
+                                      static_cast<int>(BH), p->N, num_q_tiles, args.plan_stride)))
+                return SMA_ERR_CUDA;
         }
         if (plan) {
             if (!bf16) return launch_attention<false, false, sma::kListsFromPlan>(dev, 4, tq, tk, tv, to, tm, args, stream);
@@ -419,6 +491,62 @@ int sma_attention_fwd_planned(const sma_attention_params* p, void* workspace, si
     const size_t need = attention_workspace_bytes(p->B, p->H, p->N);
     if (need != 0 && workspace_bytes < need) return SMA_ERR_WORKSPACE_TOO_SMALL;
     return attention_forward(p, static_cast<uint32_t*>(workspace), nullptr, stream_v);  // need == 0: the shape checks report it
+}
+
+// ---- backward pass -------------------------------------------------------------------------------------------
+// Workspace: delta [BH, N] fp32 (rounded up to 256 bytes), then the dQ accumulator [BH, N, 64] fp32.
+static size_t bwd_delta_bytes(long long BH, int N) { return (static_cast<size_t>(BH) * N * sizeof(float) + 255u) & ~size_t(255); }
+
+size_t sma_attention_bwd_workspace_bytes(int32_t B, int32_t H, int32_t N) {
+    if (B < 1 || H < 1 || N < 1 || N > SMA_MAX_SEQ_LEN) return 0;
+    const long long BH = 1ll * B * H;
+    if (BH * ((N + sma::kBwdBlock - 1) / sma::kBwdBlock) > 0x7FFFFFFFll) return 0;
+    return bwd_delta_bytes(BH, N) + static_cast<size_t>(BH) * N * sma::kBwdDim * sizeof(float);
+}
+
+int sma_attention_bwd(const sma_attention_params* p, const void* dout, void* dq, void* dk, void* dv, void* workspace,
+                      size_t workspace_bytes, void* stream_v) {
+    if (!p || !dout || !dq || !dk || !dv || !workspace) return SMA_ERR_NULL_POINTER;
+    if (!p->q || !p->k || !p->v || !p->mask_packed || !p->out || !p->lse) return SMA_ERR_NULL_POINTER;
+    if (p->B < 1 || p->H < 1 || p->N < 1) return SMA_ERR_BAD_SHAPE;
+    if (p->D != sma::kBwdDim) return SMA_ERR_BAD_HEAD_DIM;
+    if (p->dtype != SMA_DTYPE_F16 && p->dtype != SMA_DTYPE_BF16) return SMA_ERR_BAD_DTYPE;
+    if (p->N > SMA_MAX_SEQ_LEN) return SMA_ERR_SEQ_TOO_LONG;
+    if (!std::isfinite(p->scale) || p->scale == 0.f) return SMA_ERR_BAD_SCALE;
+    const size_t need = sma_attention_bwd_workspace_bytes(p->B, p->H, p->N);
+    if (need == 0) return SMA_ERR_BAD_SHAPE;
+    if (workspace_bytes < need) return SMA_ERR_WORKSPACE_TOO_SMALL;
+    const uintptr_t align16 = reinterpret_cast<uintptr_t>(p->q) | reinterpret_cast<uintptr_t>(p->k) |
+                              reinterpret_cast<uintptr_t>(p->v) | reinterpret_cast<uintptr_t>(p->out) |
+                              reinterpret_cast<uintptr_t>(dout) | reinterpret_cast<uintptr_t>(dq) |
+                              reinterpret_cast<uintptr_t>(dk) | reinterpret_cast<uintptr_t>(dv) |
+                              reinterpret_cast<uintptr_t>(workspace);
+    if (align16 & 15u) return SMA_ERR_MISALIGNED;
+    if ((reinterpret_cast<uintptr_t>(p->mask_packed) & 3u) || (reinterpret_cast<uintptr_t>(p->lse) & 3u)) return SMA_ERR_MISALIGNED;
+    const long long BH = 1ll * p->B * p->H;
+    const bool bf16 = p->dtype == SMA_DTYPE_BF16;
+    DeviceInfo* dev = nullptr;
+    if (int st = current_device_info(&dev)) return st;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+
+    CUtensorMap tq, tk, tv, tdo;
+    if (int st = make_qkv_tensor_map(&tq, p->q, static_cast<int>(BH), p->N, sma::kBwdBlock, bf16)) return st;
+    if (int st = make_qkv_tensor_map(&tk, p->k, static_cast<int>(BH), p->N, sma::kBwdBlock, bf16)) return st;
+    if (int st = make_qkv_tensor_map(&tv, p->v, static_cast<int>(BH), p->N, sma::kBwdBlock, bf16)) return st;
+    if (int st = make_qkv_tensor_map(&tdo, dout, static_cast<int>(BH), p->N, sma::kBwdBlock, bf16)) return st;
+
+    sma::BwdArgs args;
+    args.mask_packed = p->mask_packed;
+    args.lse = p->lse;
+    args.delta = static_cast<float*>(workspace);
+    args.dq_accum = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + bwd_delta_bytes(BH, p->N));
+    args.dk = dk;
+    args.dv = dv;
+    args.BH = static_cast<int32_t>(BH);
+    args.N = p->N;
+    args.scale = p->scale;
+    return bf16 ? launch_backward<true>(dev, tq, tk, tv, tdo, args, dout, p->out, dq, stream)
+                : launch_backward<false>(dev, tq, tk, tv, tdo, args, dout, p->out, dq, stream);
 }
 
 // ---- the entry point that allocates nothing -----------------------------------------------------------------

@@ -33,7 +33,7 @@ def sparse_attention_ref(q, k, v, mask):
 
 
 class SparseAttentionFunction(Function):
-    """autograd wrapper: CUDA forward; backward by dense recomputation in PyTorch on the same device."""
+    """autograd wrapper: CUDA forward and CUDA backward (no dense [N, N] tensor in either direction)."""
 
     @staticmethod
     def forward(ctx, q, k, v, mask_packed, mask_bool, scale, seq_len):
@@ -47,20 +47,14 @@ class SparseAttentionFunction(Function):
 
     @staticmethod
     def backward(ctx, dout):
-        # Same math as the reference's PyTorch branch (python/sparse_attention.py:96-111); the
-        # reference has no CUDA backward either (it calls a symbol its extension does not export).
+        # The reference's autograd function hands exactly these arguments to sparse_attn_cuda.backward
+        # (python/sparse_attention.py:80-94); the gradient is the one its PyTorch branch defines (:96-111).
         q, k, v, out, lse, mask_packed, mask_bool = ctx.saved_tensors
-        scale = ctx.scale
-        qf, kf, vf, dof = q.float(), k.float(), v.float(), dout.float()
-        logits = (qf @ kf.transpose(-1, -2)) * scale
-        logits = logits.masked_fill(mask_bool.logical_not(), float("-inf"))
-        attn = torch.nan_to_num(torch.softmax(logits, dim=-1), nan=0.0)
-        dv = attn.transpose(-1, -2) @ dof
-        dattn = (dof @ vf.transpose(-1, -2)).masked_fill(mask_bool.logical_not(), 0.0)
-        ds = attn * (dattn - (dattn * attn).sum(dim=-1, keepdim=True)) * scale
-        dq = ds @ kf
-        dk = ds.transpose(-1, -2) @ qf
-        return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), None, None, None, None
+        dq = torch.empty_like(q, memory_format=torch.contiguous_format)
+        dk = torch.empty_like(k, memory_format=torch.contiguous_format)
+        dv = torch.empty_like(v, memory_format=torch.contiguous_format)
+        sparse_attn_cuda.backward(dout, q, k, v, out, lse, mask_packed, dq, dk, dv, ctx.scale)
+        return dq, dk, dv, None, None, None, None
 
 
 def _check_inputs(q, k, v, mask):

@@ -133,6 +133,29 @@ def forward(q, k, v, mask_packed, out, lse, scale, is_training) -> None:
             _capi.attention_fwd(params, _stream_of(q.device))
 
 
+def backward(dout, q, k, v, out, lse, mask_packed, dq, dk, dv, scale) -> None:
+    """Gradients of the fused attention: writes ``dq``, ``dk``, ``dv`` in place.  The argument list is the one the
+    reference's autograd function passes to ``sparse_attn_cuda.backward`` (python/sparse_attention.py:90-94), a
+    function its extension never got; the gradient is that of its PyTorch branch (python/sparse_attention.py:96-111)."""
+    params, keep = _params_for(q, k, v, out, lse, scale, True)
+    B, H, N = params.B, params.H, params.N
+    for name, t in (("dout", dout), ("dq", dq), ("dk", dk), ("dv", dv)):
+        _require(t.shape == q.shape and t.dtype == q.dtype and t.device == q.device, "%s must match q" % name)
+    for name, t in (("dq", dq), ("dk", dk), ("dv", dv)):
+        _require(t.is_contiguous(), "%s must be contiguous" % name)
+    _require(mask_packed.device == q.device, "mask_packed must be on the device of q")
+    _require(mask_packed.dtype in (torch.int32, torch.uint32), "mask_packed must be int32")
+    _require(tuple(mask_packed.shape) == (B, H, N, (N + 31) // 32), "mask_packed must be [B, H, N, ceil(N/32)]")
+    dout = dout.contiguous()
+    mask_packed = mask_packed.contiguous()
+    params.mask_packed = mask_packed.data_ptr()
+    with _device_guard(q.device):
+        nbytes = _capi.attention_bwd_workspace_bytes(B, H, N)
+        workspace = torch.empty(nbytes, dtype=torch.uint8, device=q.device)  # stream-ordered: safe to drop on return
+        _capi.attention_bwd(params, dout.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), workspace.data_ptr(),
+                            nbytes, _stream_of(q.device))
+
+
 def pack_and_forward(q, k, v, mask, out, lse, scale, is_training) -> torch.Tensor:
     """``pack_mask(mask)`` followed by ``forward(...)`` with one call into the library (one trip through ctypes
     instead of two); returns the packed mask.  Not part of the reference extension's interface: the Python layer

@@ -9,6 +9,8 @@ machine without the reference's CUDA extension runs its pure-PyTorch branches:
   * sparse_attention_ref()  -> the fp32 masked-softmax oracle (:24-42)
   * sparse_attention()      -> the public entry point on CPU tensors (:120-154), incl. fp32->bf16 casting
   * SparseAttentionFunction.forward fallback (:66-74) -> the log-sum-exp values
+  * SparseAttentionFunction.backward fallback (:96-111) -> dq, dk, dv ("backward" as second argument writes only
+    backward_golden.npz)
 Inputs come from the CPU generator with fixed seeds, so they are stored only for the small cases; the
 larger case stores checksums of its inputs and the reference outputs.
 """
@@ -48,12 +50,47 @@ def lse_of(ref, q, k, v, mask, scale):
     return torch.logsumexp(s, dim=-1)
 
 
+def write_backward(ref):
+    """Gradients from the reference's own autograd function on CPU tensors (its PyTorch branches), fp32 inputs that are
+    exactly representable in fp16 so that a 16-bit kernel sees the same numbers."""
+    out = {}
+    names = []
+    g = torch.Generator().manual_seed(21)
+    cases = []
+    for name, (B, H, N, kind) in {"n8_row0_empty": (1, 1, 8, "row0"), "n64_iid": (1, 2, 64, 0.3), "n100_iid": (1, 2, 100, 0.25),
+                                  "n128_iid": (2, 2, 128, 0.25), "n200_sparse": (1, 1, 200, 0.03),
+                                  "n256_causal": (1, 2, 256, "causal"), "n72_all_false": (1, 1, 72, 0.0)}.items():
+        q, k, v, dout = [torch.randn(B, H, N, 64, generator=g).half().float() for _ in range(4)]
+        if kind == "row0":
+            m = torch.ones(B, H, N, N, dtype=torch.bool); m[:, :, 0, :] = False
+        elif kind == "causal":
+            m = torch.ones(N, N, dtype=torch.bool).tril().expand(B, H, N, N).clone()
+        else:
+            m = torch.rand(B, H, N, N, generator=g) < kind
+        cases.append((name, q, k, v, dout, m))
+    for name, q, k, v, dout, m in cases:
+        qr, kr, vr = (t.clone().requires_grad_(True) for t in (q, k, v))
+        y = ref.SparseAttentionFunction.apply(qr, kr, vr, ref.pack_mask(m), m, 0.125, q.shape[2])
+        y.backward(dout)
+        for key, t in (("q", q), ("k", k), ("v", v), ("dout", dout), ("dq", qr.grad), ("dk", kr.grad), ("dv", vr.grad)):
+            out[name + "_" + key] = t.numpy().astype(np.float16 if key in ("q", "k", "v", "dout") else np.float32)
+        out[name + "_mask"] = m.numpy()
+        names.append(name)
+    out["names"] = np.array(names)
+    np.savez_compressed(os.path.join(HERE, "backward_golden.npz"), **out)
+    print("backward_golden.npz", os.path.getsize(os.path.join(HERE, "backward_golden.npz")), "bytes")
+
+
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("SMA_REFERENCE_ROOT", "")
+    args = [a for a in sys.argv[1:] if a != "backward"]
+    root = args[0] if args else os.environ.get("SMA_REFERENCE_ROOT", "")
     if not root:
         candidates = (os.path.join(REPO, "reference"), os.path.join(os.path.dirname(REPO), "reference"))
         root = next((p for p in candidates if os.path.isdir(p)), "")
     ref = load_reference(root)
+    if "backward" in sys.argv[1:]:
+        write_backward(ref)
+        return
     sys.path.insert(0, REPO)
     from sparse_mask_attention_b200 import workloads
 
@@ -124,6 +161,7 @@ def main():
     np.savez_compressed(os.path.join(HERE, "config1_golden.npz"), **cfg1)
     for f in ("pack_golden.npz", "attention_edge_golden.npz", "config1_golden.npz"):
         print(f, os.path.getsize(os.path.join(HERE, f)), "bytes")
+    write_backward(ref)
 
 
 if __name__ == "__main__":

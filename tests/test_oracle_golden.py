@@ -1,5 +1,6 @@
 """The oracle (numpy and C restatements) against vectors written by the reference's own Python code."""
 import hashlib
+import os
 
 import numpy as np
 import torch
@@ -94,3 +95,20 @@ def test_compare_helper_flags_nan_and_excess():
     assert orc.compare(ref + 1e-3, ref)["ok"]
     assert not orc.compare(ref + np.array([0, 0.02, 0]), ref)["ok"]
     assert not orc.compare(np.array([np.nan, 1.0, -2.0]), ref)["ok"]
+
+
+def test_gradient_oracle_matches_the_reference_autograd_function():
+    """attention_bwd_np against dq, dk, dv that the reference's SparseAttentionFunction.backward produced on CPU
+    (tests/golden/make_golden.py backward): fp32 arithmetic there, fp64 here."""
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "backward_golden.npz"))
+    assert len(g["names"]) >= 6
+    for name in g["names"]:
+        dq, dk, dv = orc.attention_bwd_np(g[name + "_q"], g[name + "_k"], g[name + "_v"], g[name + "_mask"],
+                                          g[name + "_dout"], 0.125)
+        for got, key in ((dq, "dq"), (dk, "dk"), (dv, "dv")):
+            ref = g["%s_%s" % (name, key)]
+            assert np.abs(got - ref).max() <= 1e-5 * max(1.0, np.abs(ref).max()), "%s %s" % (name, key)
+    # rows that keep nothing pass no gradient
+    dq, _, _ = orc.attention_bwd_np(g["n8_row0_empty_q"], g["n8_row0_empty_k"], g["n8_row0_empty_v"],
+                                    g["n8_row0_empty_mask"], g["n8_row0_empty_dout"], 0.125)
+    assert (dq[:, :, 0] == 0).all()
