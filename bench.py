@@ -441,6 +441,41 @@ def main():
         for p in (0.05, 0.5, 1.0):
             measure_config("keep_prob_%g" % p, dataclasses.replace(base5, name="cfg5_shard_keep%g" % p, keep_prob=p), 2, 20)
 
+        # ---- the backward pass at the bench workload (not part of the headline metric, which is forward only) ----
+        def measure_backward():
+            q0, k0, v0, m0 = sets[0]
+            packed0 = sparse_attn_cuda.pack_mask(m0)
+            out0 = torch.empty_like(q0)
+            lse0 = torch.empty((B, H, N), dtype=torch.float32, device=dev)
+            scale = 64 ** -0.5
+            sparse_attn_cuda.forward(q0, k0, v0, packed0, out0, lse0, scale, True)
+            dout = torch.randn_like(q0)
+            dq, dk, dv = (torch.empty_like(q0) for _ in range(3))
+            ms = alone_ms(lambda i: sparse_attn_cuda.backward(dout, q0, k0, v0, out0, lse0, packed0, dq, dk, dv, scale), 20)
+            _capi.device_status()
+            flops = 2.5 * skip_flops  # five products per visited tile against the forward pass's two
+            res = {"ms_per_call": ms, "kernels": "bwd_prepare_kernel + attn_bwd_kernel + bwd_finish_kernel",
+                   "skip_adjusted_flops": flops, "achieved_tflops": flops / (ms * 1e-3) / 1e12,
+                   "frac": flops / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"], "timed": "20 calls back to back"}
+            try:  # the PyTorch formulation that the reference's autograd function falls back to (dense [B,H,N,N] fp32)
+                def dense(i):
+                    s_ = (q0.float() @ k0.float().transpose(-1, -2)) * scale
+                    a_ = torch.nan_to_num(torch.softmax(s_.masked_fill(~m0, float("-inf")), dim=-1), nan=0.0)
+                    dv_ = a_.transpose(-1, -2) @ dout.float()
+                    da_ = (dout.float() @ v0.float().transpose(-1, -2)).masked_fill(~m0, 0.0)
+                    ds_ = a_ * (da_ - (da_ * a_).sum(dim=-1, keepdim=True)) * scale
+                    return ds_ @ k0.float(), ds_.transpose(-1, -2) @ q0.float(), dv_
+                res["torch_dense_recompute_ms"] = alone_ms(dense, 5)
+            except Exception as e:
+                res["torch_dense_recompute_ms"] = repr(e)[:120]
+            return res
+
+        try:
+            other_configs["backward"] = measure_backward()
+        except Exception as e:
+            other_configs["backward"] = {"error": repr(e)[:200]}
+        torch.cuda.empty_cache()
+
         comparators = {}
         q0, k0, v0, m0 = sets[0]
         try:
