@@ -13,8 +13,9 @@
 //   bwd_prepare_kernel  delta = rowsum(dO o O) in fp32 and zeroes of the fp32 dQ accumulator (one warp per row)
 //   attn_bwd_kernel     one CTA per (batch*head, block of 128 keys).  It keeps K_j and V_j in shared memory, walks
 //                       the blocks of 128 query rows that keep anything in its 128 keys, and per such block issues
-//                       five tcgen05 products: S = Q K^T and dP = dO V^T into tensor memory; four warps (one
-//                       thread per query row) turn them into P and dS, written as 16-bit tiles into shared memory;
+//                       five tcgen05 products: S = Q K^T and dP = dO V^T into tensor memory; eight warps (two
+//                       threads per query row, 64 keys each) turn them into P and dS, written as 16-bit tiles into
+//                       shared memory;
 //                       dV += P^T dO and dK += dS^T Q accumulate in tensor memory over the whole walk, dQ_i = dS K
 //                       goes to tensor memory and from there, by vector atomics, into the fp32 accumulator (each row
 //                       of dQ receives one contribution per key block).  At the end dK_j, dV_j are rounded and stored.
@@ -39,7 +40,7 @@ namespace sma {
 
 constexpr int kBwdBlock = 128;              // query rows per step, and keys per CTA
 constexpr int kBwdDim = 64;                 // head dimension
-constexpr int kBwdComputeWarps = 4;         // one thread per query row
+constexpr int kBwdComputeWarps = 8;         // two threads per query row: 64 keys each
 constexpr int kBwdThreads = 32 * (kBwdComputeWarps + 1);  // + the warp that loads and issues
 constexpr uint32_t kBwdTileBytes = kBwdBlock * kBwdDim * 2;  // [128 rows][64] 16-bit
 constexpr uint32_t kBwdPanelBytes = kBwdBlock * 128;         // [128 query rows][64 keys] 16-bit
@@ -155,8 +156,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     // ---- which query blocks keep anything in keys 128j..128j+127: thread t looks at row t of every block ----
     const uint32_t* mask_bh = args.mask_packed + static_cast<size_t>(bh) * N * nw;
     if (warp < kBwdComputeWarps) {
-        for (int i = 0; i < nblk; ++i) {
-            const int row = i * kBwdBlock + static_cast<int>(threadIdx.x);
+        for (int i = warp >> 2; i < nblk; i += 2) {  // warps 0-3 take the even blocks, warps 4-7 the odd ones
+            const int row = i * kBwdBlock + static_cast<int>(threadIdx.x & 127u);
             uint32_t any = 0u;
             if (row < N) {
 #pragma unroll
@@ -264,32 +265,35 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             i = i_next;
         }
     } else {
-        // ============================== one thread per query row: P, dS, dQ, and at the end dK, dV ==============================
-        const int t = static_cast<int>(threadIdx.x);
-        const uint32_t tmem_lane = tmem + (static_cast<uint32_t>(32 * warp) << 16);
+        // ================= two threads per query row (64 keys each): P, dS, dQ, and at the end dK, dV =================
+        // Warps 0-3 take keys 0..63 of the block (panel 0), columns 0..31 of dQ and, at the end, dK; warps 4-7 keys
+        // 64..127, columns 32..63 of dQ and dV.  A warp reaches the tensor-memory lanes 32 (warp % 4) .. + 31.
+        const int t = static_cast<int>(threadIdx.x & 127u);
+        const uint32_t half = threadIdx.x >> 7;
+        const uint32_t tmem_lane = tmem + (static_cast<uint32_t>(32 * (warp & 3)) << 16);
         const float scale_log2e = args.scale * 1.4426950408889634f;
-        const uint32_t a_p = smem_u32(sm.p[0]), a_ds = smem_u32(sm.ds[0]);
-        const uint32_t row_off = static_cast<uint32_t>(t) * 128u, sw = static_cast<uint32_t>(t) & 7u;
+        const uint32_t a_p = smem_u32(sm.p[half]) + static_cast<uint32_t>(t) * 128u;
+        const uint32_t a_ds = smem_u32(sm.ds[half]) + static_cast<uint32_t>(t) * 128u;
+        const uint32_t sw = static_cast<uint32_t>(t) & 7u;
         int prev_row = 0;
         // dQ of a finished step: tensor memory -> fp32 accumulator in global memory
         auto flush_dq = [&](uint32_t step, int row) {
             wait(a_bar_mma2, step & 1u);
             tc_fence_after_sync();
             if (!ok) return;
-            float dq[kBwdDim];
-            tmem_ld32_f32(tmem_lane + kBwdColDQ, &dq[0]);
-            tmem_ld32_f32(tmem_lane + kBwdColDQ + 32, &dq[32]);
+            float dq[32];
+            tmem_ld32_f32(tmem_lane + kBwdColDQ + 32 * half, dq);
             tmem_wait_ld();
             if (row < N) {
-                float4* dst = reinterpret_cast<float4*>(args.dq_accum + (static_cast<size_t>(bh) * N + row) * kBwdDim);
+                float4* dst = reinterpret_cast<float4*>(args.dq_accum + (static_cast<size_t>(bh) * N + row) * kBwdDim + 32 * half);
 #pragma unroll
-                for (int c = 0; c < kBwdDim / 4; ++c) atomicAdd(dst + c, make_float4(dq[4 * c], dq[4 * c + 1], dq[4 * c + 2], dq[4 * c + 3]));
+                for (int c = 0; c < 8; ++c) atomicAdd(dst + c, make_float4(dq[4 * c], dq[4 * c + 1], dq[4 * c + 2], dq[4 * c + 3]));
             }
         };
         int i = next_block(0);
         while (i < nblk && ok) {
             const int row = i * kBwdBlock + t;
-            uint32_t mw[4] = {0u, 0u, 0u, 0u};
+            uint32_t mw[2] = {0u, 0u};
             float neg_lse_l2 = 0.f, delta = 0.f;
             if (row < N) {
                 const float lse = args.lse[static_cast<size_t>(bh) * N + row];
@@ -297,22 +301,23 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 if (lse != -INFINITY) {  // a row that keeps nothing has P = 0 everywhere
                     neg_lse_l2 = -lse * 1.4426950408889634f;
 #pragma unroll
-                    for (int w = 0; w < 4; ++w) {
-                        const int wi = 4 * j + w;
+                    for (int w = 0; w < 2; ++w) {
+                        const int wi = 4 * j + 2 * static_cast<int>(half) + w;
                         if (wi < nw) mw[w] = ldg_u32(mask_bh + static_cast<size_t>(row) * nw + wi);
                     }
                 }
             }
+            // the products of the step before read P and dS from shared memory and wrote dQ: both must be over; the
+            // atomics of its dQ run while the tensor core works on this step's S and dP
+            if (steps >= 1) flush_dq(steps - 1, prev_row);
             wait(a_bar_sdp, steps & 1u);
             tc_fence_after_sync();
-            // the products of the step before read P and dS from shared memory and wrote dQ: both must be over
-            if (steps >= 1) flush_dq(steps - 1, prev_row);
             if (!ok) break;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {  // 32 keys at a time
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {  // 32 keys at a time
                 float s[32], dp[32];
-                tmem_ld32_f32(tmem_lane + kBwdColS + 32 * c, s);
-                tmem_ld32_f32(tmem_lane + kBwdColDP + 32 * c, dp);
+                tmem_ld32_f32(tmem_lane + kBwdColS + 64 * half + 32 * c, s);
+                tmem_ld32_f32(tmem_lane + kBwdColDP + 64 * half + 32 * c, dp);
                 tmem_wait_ld();
                 const uint32_t bits = mw[c];
                 uint32_t pw[16], dw[16];
@@ -324,14 +329,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                     pw[e >> 1] = kBf16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
                     dw[e >> 1] = kBf16 ? pack_bf16x2(d0, d1) : pack_f16x2(d0, d1);
                 }
-                // 32 keys = four 16-byte pieces of this thread's 128-byte row in panel c / 2, pieces 4 (c % 2) .. + 3,
-                // each stored where the 128-byte swizzle puts it
-                const uint32_t panel = static_cast<uint32_t>(c >> 1) * kBwdPanelBytes + row_off;
+                // 32 keys = four 16-byte pieces of this thread's 128-byte row in its panel, pieces 4 c .. 4 c + 3, each
+                // stored where the 128-byte swizzle puts it
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
-                    const uint32_t piece = ((static_cast<uint32_t>(4 * (c & 1) + g)) ^ sw) * 16u;
-                    sts_v4(a_p + panel + piece, make_uint4(pw[4 * g], pw[4 * g + 1], pw[4 * g + 2], pw[4 * g + 3]));
-                    sts_v4(a_ds + panel + piece, make_uint4(dw[4 * g], dw[4 * g + 1], dw[4 * g + 2], dw[4 * g + 3]));
+                    const uint32_t piece = ((static_cast<uint32_t>(4 * c + g)) ^ sw) * 16u;
+                    sts_v4(a_p + piece, make_uint4(pw[4 * g], pw[4 * g + 1], pw[4 * g + 2], pw[4 * g + 3]));
+                    sts_v4(a_ds + piece, make_uint4(dw[4 * g], dw[4 * g + 1], dw[4 * g + 2], dw[4 * g + 3]));
                 }
             }
             fence_proxy_async_smem();
@@ -342,34 +346,27 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             i = next_block(i + 1);
         }
         if (steps >= 1 && ok) flush_dq(steps - 1, prev_row);
-        // ---- dK_j and dV_j: tensor-memory lane t is key 128 j + t ----
+        // ---- dK_j (warps 0-3) and dV_j (warps 4-7): tensor-memory lane t is key 128 j + t ----
         const int key = j * kBwdBlock + t;
         if (ok) {
-            uint32_t outk[kBwdDim / 2], outv[kBwdDim / 2];
+            uint32_t outw[kBwdDim / 2];
             if (steps >= 1) {
                 float acc[kBwdDim];
-                tmem_ld32_f32(tmem_lane + kBwdColDK, &acc[0]);
-                tmem_ld32_f32(tmem_lane + kBwdColDK + 32, &acc[32]);
+                const uint32_t col = half ? kBwdColDV : kBwdColDK;
+                tmem_ld32_f32(tmem_lane + col, &acc[0]);
+                tmem_ld32_f32(tmem_lane + col + 32, &acc[32]);
                 tmem_wait_ld();
 #pragma unroll
-                for (int e = 0; e < kBwdDim; e += 2) outk[e >> 1] = kBf16 ? pack_bf16x2(acc[e], acc[e + 1]) : pack_f16x2(acc[e], acc[e + 1]);
-                tmem_ld32_f32(tmem_lane + kBwdColDV, &acc[0]);
-                tmem_ld32_f32(tmem_lane + kBwdColDV + 32, &acc[32]);
-                tmem_wait_ld();
-#pragma unroll
-                for (int e = 0; e < kBwdDim; e += 2) outv[e >> 1] = kBf16 ? pack_bf16x2(acc[e], acc[e + 1]) : pack_f16x2(acc[e], acc[e + 1]);
+                for (int e = 0; e < kBwdDim; e += 2) outw[e >> 1] = kBf16 ? pack_bf16x2(acc[e], acc[e + 1]) : pack_f16x2(acc[e], acc[e + 1]);
             } else {
 #pragma unroll
-                for (int e = 0; e < kBwdDim / 2; ++e) outk[e] = outv[e] = 0u;  // no query row keeps any of these keys
+                for (int e = 0; e < kBwdDim / 2; ++e) outw[e] = 0u;  // no query row keeps any of these keys
             }
             if (key < N) {
-                uint4* pk = reinterpret_cast<uint4*>(static_cast<uint8_t*>(args.dk) + (static_cast<size_t>(bh) * N + key) * kBwdDim * 2);
-                uint4* pv = reinterpret_cast<uint4*>(static_cast<uint8_t*>(args.dv) + (static_cast<size_t>(bh) * N + key) * kBwdDim * 2);
+                uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(half ? args.dv : args.dk) +
+                                                      (static_cast<size_t>(bh) * N + key) * kBwdDim * 2);
 #pragma unroll
-                for (int c = 0; c < kBwdDim / 8; ++c) {
-                    pk[c] = make_uint4(outk[4 * c], outk[4 * c + 1], outk[4 * c + 2], outk[4 * c + 3]);
-                    pv[c] = make_uint4(outv[4 * c], outv[4 * c + 1], outv[4 * c + 2], outv[4 * c + 3]);
-                }
+                for (int c = 0; c < kBwdDim / 8; ++c) dst[c] = make_uint4(outw[4 * c], outw[4 * c + 1], outw[4 * c + 2], outw[4 * c + 3]);
             }
         }
     }
