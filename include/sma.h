@@ -20,7 +20,7 @@
 extern "C" {
 #endif
 
-#define SMA_ABI_VERSION 2
+#define SMA_ABI_VERSION 3
 
 typedef enum sma_status {
     SMA_OK                 = 0,
@@ -123,8 +123,14 @@ int sma_attention_fwd(const sma_attention_params* params, void* stream);
  * tile_bits: NULL, or a device buffer of sma_tile_bits_bytes(B, H, N) bytes; with it the two kernels work as
  * sma_pack_mask_tiles and sma_attention_fwd_tiles do (below).  A buffer given for a shape that has no side-band
  * (sma_tile_bits_bytes() == 0, or a mask that is not 32-byte aligned) is ignored.
+ * work_counter: NULL, or 4 bytes of device memory (4-byte aligned, contents do not matter) that belong to this
+ * call until its kernels have run.  With it the attention kernel's CTAs take their work items (blocks of 128 query
+ * rows) from one queue instead of a fixed share each, which evens out masks whose row blocks keep different
+ * numbers of key tiles (block-sparse, causal): the packing kernel zeroes the word, the attention kernel counts in
+ * it.  Results do not depend on it.
  */
-int sma_sparse_attention_fwd(const sma_attention_params* params, const uint8_t* mask, void* tile_bits, void* stream);
+int sma_sparse_attention_fwd(const sma_attention_params* params, const uint8_t* mask, void* tile_bits,
+                             void* work_counter, void* stream);
 
 /*
  * Packing that also tells the attention kernel where the mask keeps anything.
@@ -156,7 +162,9 @@ int sma_attention_fwd_tiles(const sma_attention_params* params, const void* tile
  * empty, that search costs more than the attention itself.  Here a small kernel computes all tile lists first,
  * with the whole GPU, into `workspace` (device memory, 16-byte aligned, at least
  * sma_attention_workspace_bytes(B, H, N) bytes, owned by the caller and free again when the call's work on the
- * stream has finished).  Results are identical to sma_attention_fwd.
+ * stream has finished).  The workspace's last 16 bytes hold the word through which the attention kernel's CTAs
+ * share out the work items (see work_counter of sma_sparse_attention_fwd).  Results are identical to
+ * sma_attention_fwd.
  * Replaces: the tile skip of the reference kernels, which test every tile of every row block in the kernel
  * (csrc/sparse_attention.cu:243-252, 485-487).
  */
@@ -193,7 +201,8 @@ int sma_attention_bwd(const sma_attention_params* params, const void* dout, void
  * routine); inputs and outputs are the caller's, as for the other entry points.
  *
  *   - Shapes whose tile lists need more than SMA_STATIC_WORKSPACE_BYTES (sma_attention_workspace_bytes(B, H, N)
- *     tells how much) are refused with SMA_ERR_STATIC_WORKSPACE_EXCEEDED; nothing is launched.
+ *     minus the 16 bytes of its work-queue word tells how much) are refused with
+ *     SMA_ERR_STATIC_WORKSPACE_EXCEEDED; nothing is launched.
  *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
  *     current).  Make that first call outside any stream capture.
  *   - All calls on a device share the one array, and each call overwrites what the previous one left there.  Two

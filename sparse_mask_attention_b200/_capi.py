@@ -11,7 +11,7 @@ import os
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG_DIR, "libsma_b200.so")
 
-SMA_ABI_VERSION = 2
+SMA_ABI_VERSION = 3
 SMA_DTYPE_F16 = 0
 SMA_DTYPE_BF16 = 1
 SMA_VARIANT_DEFAULT = 0
@@ -106,7 +106,7 @@ def _load() -> ctypes.CDLL:
     lib.sma_attention_fwd.argtypes = [ctypes.POINTER(AttentionParams), ctypes.c_void_p]
     lib.sma_sparse_attention_fwd.restype = ctypes.c_int
     lib.sma_sparse_attention_fwd.argtypes = [ctypes.POINTER(AttentionParams), ctypes.c_void_p, ctypes.c_void_p,
-                                             ctypes.c_void_p]
+                                             ctypes.c_void_p, ctypes.c_void_p]
     lib.sma_tile_bits_bytes.restype = ctypes.c_size_t
     lib.sma_tile_bits_bytes.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]
     lib.sma_pack_mask_tiles.restype = ctypes.c_int
@@ -156,11 +156,12 @@ def attention_fwd(params: AttentionParams, stream: int) -> None:
     check(lib.sma_attention_fwd(ctypes.byref(params), stream))
 
 
-def sparse_attention_fwd(params: AttentionParams, mask_ptr: int, tile_bits_ptr, stream: int) -> None:
+def sparse_attention_fwd(params: AttentionParams, mask_ptr: int, tile_bits_ptr, work_counter_ptr, stream: int) -> None:
     """pack_mask into params.mask_packed, then the forward pass, behind one call into the library.
 
-    tile_bits_ptr: None, or a device buffer of tile_bits_bytes(B, H, N) bytes for the occupancy side-band."""
-    check(lib.sma_sparse_attention_fwd(ctypes.byref(params), mask_ptr, tile_bits_ptr, stream))
+    tile_bits_ptr: None, or a device buffer of tile_bits_bytes(B, H, N) bytes for the occupancy side-band.
+    work_counter_ptr: None, or 4 bytes of device memory for the attention kernel's work queue."""
+    check(lib.sma_sparse_attention_fwd(ctypes.byref(params), mask_ptr, tile_bits_ptr, work_counter_ptr, stream))
 
 
 def tile_bits_bytes(B: int, H: int, N: int) -> int:

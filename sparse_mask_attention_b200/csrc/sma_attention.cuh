@@ -193,6 +193,11 @@ struct AttnArgs {
     // 16-bit word per 32 consecutive packed words, bit b = words 2b, 2b+1 of them hold a set bit.  When given (N a
     // multiple of 64, kListsFromBits kernel) the loader warps derive the tile lists from it.
     const uint16_t* tile_bits;
+    // Work queue shared by all CTAs of the launch, or nullptr.  A 32-bit word that the kernel before this one in the
+    // stream (packing or tile-list kernel of the same library call) has set to zero.  With it, a stream's first
+    // work item is fixed (item = CTA + stream * grid) and every further one is taken from the queue, so CTAs whose
+    // items hold fewer tiles, or whose SM runs faster, take more of them; without it item j belongs to CTA j % grid.
+    uint32_t* work_counter;
     float* lse;
     int32_t BH;
     int32_t N;
@@ -907,9 +912,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 // next work item of this CTA for this stream, or -1 when all have been taken
                 auto take_item = [&]() -> int {
                     uint32_t k = 0;
-                    if (leader) k = atomicAdd(&sm.next_item, 1u);
-                    k = __shfl_sync(0xFFFFFFFFu, k, leader_lane);
-                    const long long it = static_cast<long long>(blockIdx.x) + static_cast<long long>(k) * gridDim.x;
+                    long long it;
+                    if (args.work_counter != nullptr) {
+                        if (leader) k = atomicAdd(args.work_counter, 1u);
+                        k = __shfl_sync(0xFFFFFFFFu, k, leader_lane);
+                        it = 2ll * gridDim.x + k;
+                    } else {
+                        if (leader) k = atomicAdd(&sm.next_item, 1u);
+                        k = __shfl_sync(0xFFFFFFFFu, k, leader_lane);
+                        it = static_cast<long long>(blockIdx.x) + static_cast<long long>(k) * gridDim.x;
+                    }
+                    return it < total_items ? static_cast<int>(it) : -1;
+                };
+                // with a work queue the first item of a stream is fixed, so that nothing waits for an atomic's round
+                // trip through global memory at the start; later items are taken one item ahead
+                auto first_item = [&]() -> int {
+                    if (args.work_counter == nullptr) return take_item();
+                    const long long it = static_cast<long long>(blockIdx.x) + static_cast<long long>(stream) * gridDim.x;
                     return it < total_items ? static_cast<int>(it) : -1;
                 };
                 // Side-band bits of chunks c0..c0+3 of a work item, as this lane sees them: lane l looks at rows l, 32+l,
@@ -958,7 +977,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                            ldg_u32(reinterpret_cast<const uint32_t*>(base + 3 * num_chunks));
                 };
                 constexpr bool from_bits = kLists == kListsFromBits;
-                int item_next = take_item();
+                int item_next = first_item();
                 uint32_t mine_next = 0u;  // lane_bits of the first four chunks of item_next, requested an item ahead
                 if (from_bits && row_bytes && item_next >= 0) mine_next = lane_bits(item_next, 0);
                 while (item_next >= 0 && ok) {

@@ -313,8 +313,8 @@ static size_t tile_bits_bytes(int32_t B, int32_t H, int32_t N) {
 }
 
 // Shared body of the packing entry points; tile_bits == nullptr: packed words only.
-static int pack_mask(const uint8_t* mask, uint32_t* packed, uint16_t* tile_bits, int32_t B, int32_t H, int32_t N,
-                     void* stream_v) {
+static int pack_mask(const uint8_t* mask, uint32_t* packed, uint16_t* tile_bits, uint32_t* work_counter, int32_t B,
+                     int32_t H, int32_t N, void* stream_v) {
     if (!mask || !packed) return SMA_ERR_NULL_POINTER;
     if (B < 1 || H < 1 || N < 1) return SMA_ERR_BAD_SHAPE;
     const unsigned long long rows = 1ull * B * H * N;
@@ -339,9 +339,9 @@ static int pack_mask(const uint8_t* mask, uint32_t* packed, uint16_t* tile_bits,
         if (blocks > 0x7FFFFFFFu) blocks = 0x7FFFFFFFu;
         const cudaError_t e =
             tile_bits ? launch_overlapped(sma::pack_flat_kernel<true>, static_cast<unsigned>(blocks), sma::kPackThreads, 0,
-                                          stream, mask, packed, tile_bits, n_words)
+                                          stream, mask, packed, tile_bits, n_words, work_counter)
                       : launch_overlapped(sma::pack_flat_kernel<false>, static_cast<unsigned>(blocks), sma::kPackThreads, 0,
-                                          stream, mask, packed, static_cast<uint16_t*>(nullptr), n_words);
+                                          stream, mask, packed, static_cast<uint16_t*>(nullptr), n_words, work_counter);
         if (!cuda_ok(e)) return SMA_ERR_CUDA;
     } else {
         const size_t warps_per_block = sma::kPackThreads / 32;
@@ -349,14 +349,14 @@ static int pack_mask(const uint8_t* mask, uint32_t* packed, uint16_t* tile_bits,
         const size_t cap = static_cast<size_t>(dev->sm_count) * 8 * 4;
         if (blocks > cap) blocks = cap;
         if (!cuda_ok(launch_overlapped(sma::pack_rows_kernel, static_cast<unsigned>(blocks), sma::kPackThreads, 0, stream,
-                                       mask, packed, static_cast<size_t>(rows), N)))
+                                       mask, packed, static_cast<size_t>(rows), N, work_counter)))
             return SMA_ERR_CUDA;
     }
     return SMA_OK;
 }
 
 int sma_pack_mask(const uint8_t* mask, uint32_t* packed, int32_t B, int32_t H, int32_t N, void* stream_v) {
-    return pack_mask(mask, packed, nullptr, B, H, N, stream_v);
+    return pack_mask(mask, packed, nullptr, nullptr, B, H, N, stream_v);
 }
 
 size_t sma_tile_bits_bytes(int32_t B, int32_t H, int32_t N) { return tile_bits_bytes(B, H, N); }
@@ -364,14 +364,15 @@ size_t sma_tile_bits_bytes(int32_t B, int32_t H, int32_t N) { return tile_bits_b
 int sma_pack_mask_tiles(const uint8_t* mask, uint32_t* packed, void* tile_bits, int32_t B, int32_t H, int32_t N,
                         void* stream_v) {
     if (!tile_bits) return SMA_ERR_NULL_POINTER;
-    return pack_mask(mask, packed, static_cast<uint16_t*>(tile_bits), B, H, N, stream_v);
+    return pack_mask(mask, packed, static_cast<uint16_t*>(tile_bits), nullptr, B, H, N, stream_v);
 }
 
 // Shared body of the attention entry points.  plan == nullptr and tile_bits == nullptr: the kernel's loader warps
 // find the non-empty tiles themselves by reading the packed mask.  plan: a workspace of at least
 // attention_workspace_bytes() bytes that the tile-list kernel fills first.  tile_bits: the occupancy side-band that
 // sma_pack_mask_tiles wrote for this mask_packed.
-static int attention_forward(const sma_attention_params* p, uint32_t* plan, const uint16_t* tile_bits, void* stream_v) {
+static int attention_forward(const sma_attention_params* p, uint32_t* plan, const uint16_t* tile_bits,
+                             uint32_t* work_counter, void* stream_v) {
     if (!p) return SMA_ERR_NULL_POINTER;
     if (!p->q || !p->k || !p->v || !p->mask_packed || !p->out) return SMA_ERR_NULL_POINTER;
     if (p->save_lse && !p->lse) return SMA_ERR_NULL_POINTER;
@@ -424,6 +425,7 @@ static int attention_forward(const sma_attention_params* p, uint32_t* plan, cons
     args.mask_packed = p->mask_packed;
     args.plan = plan;
     args.tile_bits = tile_bits;
+    args.work_counter = work_counter;
     args.plan_stride = sma::plan_stride_words(p->N);
     args.lse = p->lse;
     args.BH = static_cast<int32_t>(BH);
@@ -438,7 +440,7 @@ static int attention_forward(const sma_attention_params* p, uint32_t* plan, cons
         if (plan) {
             const unsigned items = static_cast<unsigned>(BH * num_q_tiles);
             if (!cuda_ok(launch_plain(sma::build_tile_lists_kernel, items, sma::kPlanRows, 0, stream, p->mask_packed, plan,
-                                      static_cast<int>(BH), p->N, num_q_tiles, args.plan_stride)))
+                                      static_cast<int>(BH), p->N, num_q_tiles, args.plan_stride, work_counter)))
                 return SMA_ERR_CUDA;
         }
         if (plan) {
@@ -455,32 +457,45 @@ static int attention_forward(const sma_attention_params* p, uint32_t* plan, cons
     return launch_attention<true, false, sma::kListsFromStrips>(dev, 2, tq, tk, tv, to, tm, args, stream);
 }
 
+static size_t plan_lists_bytes(long long items, int32_t N) {
+    return static_cast<size_t>(items) * sma::plan_stride_words(N) * sizeof(uint32_t);
+}
+
+// The work-queue word at the end of a tile-list workspace (zeroed by the tile-list kernel of the same call).
+static uint32_t* plan_work_counter(uint32_t* workspace, const sma_attention_params* p) {
+    const long long items = 1ll * p->B * p->H * ((p->N + sma::kBlockM - 1) / sma::kBlockM);
+    return workspace + plan_lists_bytes(items, p->N) / sizeof(uint32_t);
+}
+
 // Bytes of workspace for B x H x N, or 0 for a shape the attention entry points reject.
 static size_t attention_workspace_bytes(int32_t B, int32_t H, int32_t N) {
     if (B < 1 || H < 1 || N < 1 || N > SMA_MAX_SEQ_LEN) return 0;
     const long long items = 1ll * B * H * ((N + sma::kBlockM - 1) / sma::kBlockM);
     if (items > 0x7FFFFFFFll) return 0;
-    return static_cast<size_t>(items) * sma::plan_stride_words(N) * sizeof(uint32_t);
+    return plan_lists_bytes(items, N) + 16;  // the tile lists, then the attention kernel's work-queue word
 }
 
 int sma_attention_fwd(const sma_attention_params* p, void* stream_v) {
-    return attention_forward(p, nullptr, nullptr, stream_v);
+    return attention_forward(p, nullptr, nullptr, nullptr, stream_v);
 }
 
 int sma_attention_fwd_tiles(const sma_attention_params* p, const void* tile_bits, void* stream_v) {
     if (!tile_bits) return SMA_ERR_NULL_POINTER;
-    return attention_forward(p, nullptr, static_cast<const uint16_t*>(tile_bits), stream_v);
+    return attention_forward(p, nullptr, static_cast<const uint16_t*>(tile_bits), nullptr, stream_v);
 }
 
-int sma_sparse_attention_fwd(const sma_attention_params* p, const uint8_t* mask, void* tile_bits, void* stream_v) {
+int sma_sparse_attention_fwd(const sma_attention_params* p, const uint8_t* mask, void* tile_bits, void* work_counter,
+                             void* stream_v) {
     if (!p || !mask) return SMA_ERR_NULL_POINTER;
     if (!p->mask_packed) return SMA_ERR_NULL_POINTER;
     // the side-band exists for N % 64 == 0 and a 32-byte aligned mask; the caller who passes a buffer for another
     // shape gets the plain pair of kernels
     uint16_t* bits = static_cast<uint16_t*>(tile_bits);
     if (bits && (tile_bits_bytes(p->B, p->H, p->N) == 0 || (reinterpret_cast<uintptr_t>(mask) & 31u))) bits = nullptr;
-    if (int st = pack_mask(mask, const_cast<uint32_t*>(p->mask_packed), bits, p->B, p->H, p->N, stream_v)) return st;
-    return attention_forward(p, nullptr, bits, stream_v);
+    if (reinterpret_cast<uintptr_t>(work_counter) & 3u) return SMA_ERR_MISALIGNED;
+    uint32_t* counter = static_cast<uint32_t*>(work_counter);
+    if (int st = pack_mask(mask, const_cast<uint32_t*>(p->mask_packed), bits, counter, p->B, p->H, p->N, stream_v)) return st;
+    return attention_forward(p, nullptr, bits, counter, stream_v);
 }
 
 size_t sma_attention_workspace_bytes(int32_t B, int32_t H, int32_t N) { return attention_workspace_bytes(B, H, N); }
@@ -490,7 +505,9 @@ int sma_attention_fwd_planned(const sma_attention_params* p, void* workspace, si
     if (reinterpret_cast<uintptr_t>(workspace) & 15u) return SMA_ERR_MISALIGNED;
     const size_t need = attention_workspace_bytes(p->B, p->H, p->N);
     if (need != 0 && workspace_bytes < need) return SMA_ERR_WORKSPACE_TOO_SMALL;
-    return attention_forward(p, static_cast<uint32_t*>(workspace), nullptr, stream_v);  // need == 0: the shape checks report it
+    if (need == 0) return attention_forward(p, nullptr, nullptr, nullptr, stream_v);  // the shape checks in there report why
+    uint32_t* plan = static_cast<uint32_t*>(workspace);
+    return attention_forward(p, plan, nullptr, plan_work_counter(plan, p), stream_v);
 }
 
 // ---- backward pass -------------------------------------------------------------------------------------------
@@ -554,7 +571,8 @@ int sma_attention_bwd(const sma_attention_params* p, const void* dout, void* dq,
 // that loads the library carries these SMA_STATIC_WORKSPACE_BYTES from the first CUDA call to process exit.
 // In host code the name below only identifies the symbol; the address a kernel can use comes from
 // cudaGetSymbolAddress on the device in question.
-static __device__ __align__(256) uint32_t g_static_workspace[SMA_STATIC_WORKSPACE_BYTES / sizeof(uint32_t)];
+// (plus the 16 bytes of the attention kernel's work-queue word that every tile-list workspace ends with)
+static __device__ __align__(256) uint32_t g_static_workspace[(SMA_STATIC_WORKSPACE_BYTES + 16) / sizeof(uint32_t)];
 
 namespace {
 uint32_t* g_static_workspace_addr[kMaxDevices] = {};  // per device, resolved by the first call made on it
@@ -578,7 +596,7 @@ int static_workspace_of_current_device(uint32_t** out) {
 int sma_attention_fwd_static_workspace(const sma_attention_params* p, void* stream_v) {
     if (!p) return SMA_ERR_NULL_POINTER;
     const size_t need = attention_workspace_bytes(p->B, p->H, p->N);
-    if (need > SMA_STATIC_WORKSPACE_BYTES) return SMA_ERR_STATIC_WORKSPACE_EXCEEDED;
+    if (need > SMA_STATIC_WORKSPACE_BYTES + 16) return SMA_ERR_STATIC_WORKSPACE_EXCEEDED;
     // the device is looked at before the array's address: on a GPU for which the library holds no code the
     // caller should hear SMA_ERR_WRONG_ARCH, like from the other entry points, not a failed symbol look-up
     DeviceInfo* dev = nullptr;
@@ -587,7 +605,8 @@ int sma_attention_fwd_static_workspace(const sma_attention_params* p, void* stre
     if (int st = static_workspace_of_current_device(&workspace)) return st;
     // Nothing in the workspace has to start at zero: the tile-list kernel writes every word the attention kernel
     // reads (the count of each work item and that many entries), so the previous call's leftovers are never seen.
-    return attention_forward(p, workspace, nullptr, stream_v);  // need == 0: the shape checks in there report why
+    if (need == 0) return attention_forward(p, nullptr, nullptr, nullptr, stream_v);  // the shape checks in there report why
+    return attention_forward(p, workspace, nullptr, plan_work_counter(workspace, p), stream_v);
 }
 
 #ifdef SMA_WAIT_TEST_BUILD

@@ -68,9 +68,12 @@ __device__ __forceinline__ uint32_t even_bits(uint32_t x) {
 template <bool kTiles>
 __global__ void __launch_bounds__(kPackThreads, kPackBlocksPerSM)
 pack_flat_kernel(const uint8_t* __restrict__ mask, uint32_t* __restrict__ packed, uint16_t* __restrict__ tile_bits,
-                 size_t n_words) {
+                 size_t n_words, uint32_t* __restrict__ work_counter) {
     grid_launch_dependents();
     grid_dependency_wait();  // the mask may be the previous kernel's output
+    // the attention kernel that follows in the stream starts its work queue at zero (it reads the word only after
+    // this grid has completed; the wait above keeps the write behind an earlier kernel that may still use the word)
+    if (work_counter != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *work_counter = 0u;
     constexpr int kUnroll = pack_unroll(kTiles);
     const size_t block_words = static_cast<size_t>(kPackThreads) * kUnroll;
     const size_t stride = static_cast<size_t>(gridDim.x) * block_words;
@@ -106,9 +109,11 @@ pack_flat_kernel(const uint8_t* __restrict__ mask, uint32_t* __restrict__ packed
 
 // Row path for any N and any alignment: one warp per mask row, grid-stride over rows.
 __global__ void __launch_bounds__(kPackThreads)
-pack_rows_kernel(const uint8_t* __restrict__ mask, uint32_t* __restrict__ packed, size_t n_rows, int N) {
+pack_rows_kernel(const uint8_t* __restrict__ mask, uint32_t* __restrict__ packed, size_t n_rows, int N,
+                 uint32_t* __restrict__ work_counter) {
     grid_launch_dependents();
     grid_dependency_wait();
+    if (work_counter != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *work_counter = 0u;
     const int lane = threadIdx.x & 31;
     const int nw = (N + 31) >> 5;
     const size_t warps_total = static_cast<size_t>(gridDim.x) * (kPackThreads / 32);

@@ -36,12 +36,13 @@ __host__ __device__ constexpr uint32_t plan_stride_words(int N) {
 // Other shapes take a simple path (thread r reads row r word by word); they are short or rare.
 __global__ void __launch_bounds__(kPlanRows)
 build_tile_lists_kernel(const uint32_t* __restrict__ mask_packed, uint32_t* __restrict__ plan, int BH, int N,
-                        int num_q_tiles, uint32_t stride_words) {
+                        int num_q_tiles, uint32_t stride_words, uint32_t* __restrict__ work_counter) {
     // Launched the ordinary way (after the previous kernel has completed).  Were its CTAs allowed in early, they
     // would all gather on the few SMs that the previous kernel's first finished CTAs leave, and the attention
     // kernel's CTAs, allowed in behind them, would hold the other SMs idle while this kernel runs on a fifth of
     // the GPU.  The attention kernel may start its set-up only when this CTA's work is done (end of the kernel).
     const int item = blockIdx.x;
+    if (work_counter != nullptr && item == 0 && threadIdx.x == 0) *work_counter = 0u;  // the attention kernel's work queue
     const int bh = item % BH;
     const int row0 = (num_q_tiles - 1 - item / BH) * kPlanRows;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;

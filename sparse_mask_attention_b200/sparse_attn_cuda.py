@@ -174,8 +174,9 @@ def pack_and_forward(q, k, v, mask, out, lse, scale, is_training) -> torch.Tenso
             # the attention kernel takes its tile lists from them -- as fast as the tile-list kernel with its
             # workspace (below), with two launches instead of three and one call into the library.  Up to
             # PLAN_ABOVE_SEQ_LEN the attention kernel's own scan of the packed mask is faster than either.
-            tile_bits = torch.empty(_capi.tile_bits_bytes(B, H, N) // 2, dtype=torch.int16, device=q.device)
-            _capi.sparse_attention_fwd(params, mask.data_ptr(), tile_bits.data_ptr(), _stream_of(q.device))
+            tile_bits = torch.empty(_capi.tile_bits_bytes(B, H, N) // 2 + 2, dtype=torch.int16, device=q.device)
+            counter = tile_bits.data_ptr() + tile_bits.numel() * 2 - 4  # the attention kernel's work queue
+            _capi.sparse_attention_fwd(params, mask.data_ptr(), tile_bits.data_ptr(), counter, _stream_of(q.device))
         elif N > PLAN_ABOVE_SEQ_LEN:
             stream = _stream_of(q.device)
             _capi.pack_mask(mask.data_ptr(), packed.data_ptr(), B, H, N, stream)
@@ -183,5 +184,6 @@ def pack_and_forward(q, k, v, mask, out, lse, scale, is_training) -> torch.Tenso
             workspace = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
             _capi.attention_fwd_planned(params, workspace.data_ptr(), nbytes, stream)
         else:
-            _capi.sparse_attention_fwd(params, mask.data_ptr(), None, _stream_of(q.device))
+            counter = torch.empty(1, dtype=torch.int32, device=q.device)  # the attention kernel's work queue
+            _capi.sparse_attention_fwd(params, mask.data_ptr(), None, counter.data_ptr(), _stream_of(q.device))
     return packed

@@ -117,7 +117,7 @@ def test_pack_then_forward_into_reused_buffers_without_synchronising():
 
 
 def test_workspace_size_and_errors():
-    assert _capi.attention_workspace_bytes(16, 12, 512) == 16 * 12 * 4 * 8 * 4  # 768 items x 8 words
+    assert _capi.attention_workspace_bytes(16, 12, 512) == 16 * 12 * 4 * 8 * 4 + 16  # 768 items x 8 words + work queue
     assert _capi.attention_workspace_bytes(0, 1, 64) == 0 and _capi.attention_workspace_bytes(1, 1, 16385) == 0
     cfg = workloads.Config("planned", 1, 1, 256, torch.float16, "iid", 0.25, seed=1)
     q, k, v, mask = (t.cuda() for t in workloads.make_inputs(cfg))

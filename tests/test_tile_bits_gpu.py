@@ -118,7 +118,7 @@ def test_headline_shape_through_the_combined_call():
         p = _params(q, k, v, packed, out, lse)
         bits = torch.empty(_capi.tile_bits_bytes(B, H, N) // 2, dtype=torch.int16, device="cuda") if with_bits else None
         for _ in range(3):  # queued without synchronising: each call's attention kernel must see its own bits
-            _capi.sparse_attention_fwd(p, mask.data_ptr(), bits.data_ptr() if with_bits else None, None)
+            _capi.sparse_attention_fwd(p, mask.data_ptr(), bits.data_ptr() if with_bits else None, None, None)
         torch.cuda.synchronize()
         _capi.device_status()
         outs.append((out, lse, packed))
@@ -154,7 +154,7 @@ def test_shapes_without_a_side_band_are_refused():
     lse = torch.empty((B, H, N), dtype=torch.float32, device="cuda")
     p = _params(qd, kd, vd, packed, out, lse)
     big_bits = torch.empty(_capi.tile_bits_bytes(B, H, N) // 2, dtype=torch.int16, device="cuda")
-    _capi.sparse_attention_fwd(p, buf.data_ptr() + 16, big_bits.data_ptr(), None)
+    _capi.sparse_attention_fwd(p, buf.data_ptr() + 16, big_bits.data_ptr(), None, None)
     torch.cuda.synchronize()
     _capi.device_status()
     ref, _ = gu.oracle_for(q, k, v, mask)
