@@ -762,26 +762,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                     __syncwarp();
                 };
                 // Non-empty tiles of the chunk whose strip sits in `slot`, written into the slot's descriptor; returns
-                // their number.  Lane l looks at rows l, 32+l, 64+l, 96+l.
+                // their number.  The strip is read as 16 runs of 512 consecutive bytes (eight rows), lane l taking the
+                // l-th 16-byte piece of a run: row 8 i + l / 4, key tiles 2 (l % 4) and 2 (l % 4) + 1.  (Consecutive
+                // lanes on consecutive pieces: a lane per row, 64 bytes apart, put four lanes on every bank.)
                 auto list_from_strip = [&](uint32_t slot, int c) -> uint32_t {
                     const uint4* strip = reinterpret_cast<const uint4*>(tl.strip[slot]);
                     uint32_t grp[4];
 #pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        uint4 x[8];  // two row groups at a time: eight loads in flight
+                    for (int g = 0; g < 4; ++g) {  // one group of 32 rows = four runs
+                        uint4 x[4];
 #pragma unroll
-                        for (int i = 0; i < 8; ++i)
-                            x[i] = strip[((2 * half + (i >> 2)) * 32 + lane) * (kStripRowBytes / 16) + (i & 3)];
-#pragma unroll
-                        for (int gq = 0; gq < 2; ++gq) {
-                            uint32_t mine = 0;
-#pragma unroll
-                            for (int k = 0; k < 4; ++k) {
-                                if ((x[4 * gq + k].x | x[4 * gq + k].y) != 0u) mine |= 1u << (2 * k);
-                                if ((x[4 * gq + k].z | x[4 * gq + k].w) != 0u) mine |= 2u << (2 * k);
-                            }
-                            grp[2 * half + gq] = __reduce_or_sync(0xFFFFFFFFu, mine);
-                        }
+                        for (int k = 0; k < 4; ++k) x[k] = strip[(4 * g + k) * 32 + lane];
+                        const uint32_t lo = x[0].x | x[0].y | x[1].x | x[1].y | x[2].x | x[2].y | x[3].x | x[3].y;
+                        const uint32_t hi = x[0].z | x[0].w | x[1].z | x[1].w | x[2].z | x[2].w | x[3].z | x[3].w;
+                        const uint32_t mine = ((lo != 0u ? 1u : 0u) | (hi != 0u ? 2u : 0u)) << (2 * (lane & 3));
+                        grp[g] = __reduce_or_sync(0xFFFFFFFFu, mine);
                     }
                     const uint32_t any = grp[0] | grp[1] | grp[2] | grp[3];
                     if (lane < kChunkTiles && ((any >> lane) & 1u)) {
