@@ -48,8 +48,8 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the ncu captures summarised under
 # profiles/ — figures of those captures, not of this run; `traffic_source` in the JSON line names the file.
 NCU_TRAFFIC = {
-    ("attn", 2): (44_122_368 + 650_752, "profiles/attn_fwd_headline_B16_H12_N512.md"),
-    ("pack", 2): (50_336_000 + 52_992, "profiles/pack_flat_headline_B16_H12_N512.md"),
+    ("attn", 2): (44_119_040 + 442_112, "profiles/attn_fwd_headline_B16_H12_N512.md"),
+    ("pack", 2): (50_335_744 + 84_608, "profiles/pack_flat_headline_B16_H12_N512.md"),
 }
 
 

@@ -487,6 +487,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                                 }
                             };
                             if ((e_cur >> (8 + wq)) & 1u) {
+                                // (rows are 64 bytes apart, so the lanes of this load meet on two pairs of banks; with the
+                                // strip in the 64-byte swizzle they spread over eight, and the launch took as long or longer)
                                 const uint2 w = lds_v2(a_row + ((e_cur & (kChunkTiles - 1)) << 3));
                                 const bool next_ready = have_next && mbar_test_wait_a(next_bar, nphase);
                                 [[maybe_unused]] bool turn_ready = false;
