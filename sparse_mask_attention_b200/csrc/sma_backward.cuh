@@ -15,10 +15,13 @@
 //                       the blocks of 128 query rows that keep anything in its 128 keys, and per such block issues
 //                       five tcgen05 products: S = Q K^T and dP = dO V^T into tensor memory; eight warps (two
 //                       threads per query row, 64 keys each) turn them into P and dS, written as 16-bit tiles into
-//                       shared memory;
-//                       dV += P^T dO and dK += dS^T Q accumulate in tensor memory over the whole walk, dQ_i = dS K
-//                       goes to tensor memory and from there, by vector atomics, into the fp32 accumulator (each row
-//                       of dQ receives one contribution per key block).  At the end dK_j, dV_j are rounded and stored.
+//                       shared memory; dV += P^T dO and dK += dS^T Q accumulate in tensor memory over the whole walk,
+//                       dQ_i = dS K goes to tensor memory and from there, through a staging tile in shared memory and
+//                       a TMA reduction (fp32 add), into the accumulator (each row of dQ receives one contribution
+//                       per key block).  At the end dK_j, dV_j are rounded and stored.
+//                       The walk is software-pipelined: P/dS, Q/dO and dQ exist twice, S and dP of block s+1 are
+//                       issued as soon as the compute warps have read those of block s out of tensor memory, and the
+//                       three products that consume P and dS of block s run under the arithmetic of block s+1.
 //   bwd_finish_kernel   dq = round(accumulator)
 //
 // P and dS are the A operands of products that contract over the query rows (P^T, dS^T: "MN-major" operands, read
@@ -26,8 +29,8 @@
 // panels of [128 query rows][64 keys] 16-bit values, rows of 128 bytes with the 128-byte swizzle, the second panel
 // 16 KB behind the first (the leading byte offset of the MN-major descriptor).
 //
-// dQ is summed by atomics in fp32: its last bits depend on the order in which CTAs arrive, so it is reproducible
-// to rounding, not bit for bit.  dK and dV are deterministic.
+// dQ is summed in fp32 in the order in which the CTAs' reductions arrive: its last bits can differ from run to run,
+// so it is reproducible to rounding, not bit for bit.  dK and dV are deterministic.
 #pragma once
 
 #include <cuda.h>
@@ -45,7 +48,7 @@ constexpr int kBwdThreads = 32 * (kBwdComputeWarps + 1);  // + the warp that loa
 constexpr uint32_t kBwdTileBytes = kBwdBlock * kBwdDim * 2;  // [128 rows][64] 16-bit
 constexpr uint32_t kBwdPanelBytes = kBwdBlock * 128;         // [128 query rows][64 keys] 16-bit
 constexpr uint32_t kBwdTmemCols = 512;
-constexpr uint32_t kBwdColS = 0, kBwdColDP = 128, kBwdColDV = 256, kBwdColDK = 320, kBwdColDQ = 384;
+constexpr uint32_t kBwdColS = 0, kBwdColDP = 128, kBwdColDV = 256, kBwdColDK = 320, kBwdColDQ = 384;  // dQ: two buffers of 64
 constexpr int kBwdMaxQBlocks = 16384 / kBwdBlock;
 
 struct BwdSmem {
@@ -53,13 +56,17 @@ struct BwdSmem {
     alignas(1024) uint8_t v[kBwdTileBytes];
     alignas(1024) uint8_t q[2][kBwdTileBytes];
     alignas(1024) uint8_t dout[2][kBwdTileBytes];
-    alignas(1024) uint8_t p[2][kBwdPanelBytes];   // two panels of 64 keys
-    alignas(1024) uint8_t ds[2][kBwdPanelBytes];
+    alignas(1024) uint8_t p[2][2][kBwdPanelBytes];   // [step % 2][panel of 64 keys]
+    alignas(1024) uint8_t ds[2][2][kBwdPanelBytes];
     uint64_t bar_kv;        // TMA: K_j and V_j landed
     uint64_t bar_qdo[2];    // TMA: Q_i and dO_i landed in stage s
     uint64_t bar_sdp;       // tensor core: S and dP of the step are complete
-    uint64_t bar_pds;       // 128 arrivals: P and dS of the step are in shared memory (and S, dP, dQ have been read)
+    uint64_t bar_sfree;     // all compute threads: S and dP of the step have been read out of tensor memory
+    uint64_t bar_pds;       // all compute threads: P and dS of the step are in shared memory, its S and dP and the
+                            // dQ of the step before have been read out of tensor memory
     uint64_t bar_mma2;      // tensor core: dV, dK accumulated and dQ complete for the step
+    uint64_t bar_half[2];   // the 128 compute threads of a half meet here (a bounded wait, unlike bar.sync)
+    uint64_t bar_qdo_free;  // tensor core: the products that read the step's Q and dO tiles (dV, dK) are complete
     uint32_t tmem_base;
     uint32_t abort_flag;
     uint32_t qblock_any[kBwdMaxQBlocks / 32];  // bit i: query block i keeps something in this CTA's keys
@@ -120,7 +127,7 @@ template <bool kBf16>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
-                const BwdArgs args) {
+                const __grid_constant__ CUtensorMap tmap_dq, const BwdArgs args) {
     extern __shared__ uint8_t smem_raw[];
     BwdSmem& sm = *reinterpret_cast<BwdSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~static_cast<uintptr_t>(1023u));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -137,8 +144,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         mbar_init(&sm.bar_qdo[0], 1);
         mbar_init(&sm.bar_qdo[1], 1);
         mbar_init(&sm.bar_sdp, 1);
+        mbar_init(&sm.bar_sfree, 32 * kBwdComputeWarps);
         mbar_init(&sm.bar_pds, 32 * kBwdComputeWarps);
         mbar_init(&sm.bar_mma2, 1);
+        mbar_init(&sm.bar_qdo_free, 1);
+        mbar_init(&sm.bar_half[0], 128);
+        mbar_init(&sm.bar_half[1], 128);
         sm.abort_flag = 0u;
         for (int i = 0; i < kBwdMaxQBlocks / 32; ++i) sm.qblock_any[i] = 0u;
         mbar_init_fence();
@@ -155,25 +166,45 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 
     // ---- which query blocks keep anything in keys 128j..128j+127: thread t looks at row t of every block ----
     const uint32_t* mask_bh = args.mask_packed + static_cast<size_t>(bh) * N * nw;
+    // Plain loads (this kernel is launched the ordinary way: everything written before it is visible), and all loads of
+    // a batch of four blocks before the first ballot: the shared-memory atomic below keeps the compiler from moving
+    // later loads above it, and one block at a time the scan paid a full memory latency per block.
     if (warp < kBwdComputeWarps) {
-        for (int i = warp >> 2; i < nblk; i += 2) {  // warps 0-3 take the even blocks, warps 4-7 the odd ones
-            const int row = i * kBwdBlock + static_cast<int>(threadIdx.x & 127u);
-            uint32_t any = 0u;
-            if (row < N) {
+        const int trow = static_cast<int>(threadIdx.x & 127u);
+        for (int i0 = warp >> 2; i0 < nblk; i0 += 8) {  // warps 0-3 take the even blocks, warps 4-7 the odd ones
+            uint32_t any[4];
 #pragma unroll
-                for (int w = 0; w < 4; ++w) {
-                    const int wi = 4 * j + w;
-                    if (wi < nw) any |= ldg_u32(mask_bh + static_cast<size_t>(row) * nw + wi);
+            for (int b = 0; b < 4; ++b) {
+                const int i = i0 + 2 * b, row = i * kBwdBlock + trow;
+                any[b] = 0u;
+                if (i < nblk && row < N) {
+                    const uint32_t* mrow = mask_bh + static_cast<size_t>(row) * nw + 4 * j;
+#pragma unroll
+                    for (int w = 0; w < 4; ++w)
+                        if (4 * j + w < nw) any[b] |= mrow[w];
                 }
             }
-            const uint32_t some = __ballot_sync(0xFFFFFFFFu, any != 0u);
-            if (lane == 0 && some != 0u) atomicOr(&sm.qblock_any[i >> 5], 1u << (i & 31));
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                const int i = i0 + 2 * b;
+                const uint32_t some = __ballot_sync(0xFFFFFFFFu, any[b] != 0u);
+                if (lane == 0 && some != 0u) atomicOr(&sm.qblock_any[i >> 5], 1u << (i & 31));
+            }
         }
+    } else {
+        // meanwhile the control warp asks for K_j and V_j, which every CTA with work needs whatever the scan finds
+        if (lane == 0) {
+            const uint32_t bar = smem_u32(&sm.bar_kv);
+            mbar_arrive_expect_tx_a(bar, 2 * kBwdTileBytes);
+            tma_load_3d_a(smem_u32(sm.k), &tmap_k, bar, 0, j * kBwdBlock, bh);
+            tma_load_3d_a(smem_u32(sm.v), &tmap_v, bar, 0, j * kBwdBlock, bh);
+        }
+        __syncwarp();
     }
     __syncthreads();
 
     const uint32_t a_bar_kv = smem_u32(&sm.bar_kv), a_bar_qdo = smem_u32(&sm.bar_qdo[0]), a_bar_sdp = smem_u32(&sm.bar_sdp),
-                   a_bar_pds = smem_u32(&sm.bar_pds), a_bar_mma2 = smem_u32(&sm.bar_mma2);
+                   a_bar_pds = smem_u32(&sm.bar_pds), a_bar_mma2 = smem_u32(&sm.bar_mma2), a_bar_sfree = smem_u32(&sm.bar_sfree);
     bool ok = true;  // false once a bounded wait has run out; the same in all lanes of a warp
     auto wait = [&](uint32_t bar, uint32_t parity) {
         if (ok) ok = __all_sync(0xFFFFFFFFu, mbar_wait_a(bar, parity, abort_flag));
@@ -187,16 +218,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     uint32_t steps = 0;  // query blocks walked
     if (warp == kBwdComputeWarps) {
         // ===================================== loads and tensor-core issue =====================================
-        const bool leader = lane == 0;
+        // all lanes run the control flow (operands stay in uniform registers); one elected lane issues
+        const bool leader = elect_one();
         constexpr uint32_t kHi = kSmemDescSw128Hi;
         constexpr uint32_t idesc_s = make_idesc(kFmt, kFmt, kMajorK, kMajorK, kBwdBlock, kBwdBlock, 0);    // [128 q][128 keys]
         constexpr uint32_t idesc_t = make_idesc(kFmt, kFmt, kMajorMN, kMajorMN, kBwdBlock, kBwdDim, 0);    // (P|dS)^T [128 keys][64]
         constexpr uint32_t idesc_q = make_idesc(kFmt, kFmt, kMajorK, kMajorMN, kBwdBlock, kBwdDim, 0);     // dS K [128 q][64]
         constexpr uint32_t kPanelLbo = (kBwdPanelBytes >> 4) << 16;  // second panel of 64 keys, for the transposed reads
         const uint32_t k_lo = smem_desc_sw128_lo(smem_u32(sm.k)), v_lo = smem_desc_sw128_lo(smem_u32(sm.v));
-        const uint32_t p_t_lo = ((smem_u32(sm.p[0]) & 0x3FFFFu) >> 4) | kPanelLbo;
-        const uint32_t ds_t_lo = ((smem_u32(sm.ds[0]) & 0x3FFFFu) >> 4) | kPanelLbo;
-        const uint32_t ds_k_lo = smem_desc_sw128_lo(smem_u32(sm.ds[0]));
+        constexpr uint32_t kStageUnits = (2 * kBwdPanelBytes) >> 4;  // from one P/dS buffer to the other, in descriptor units
+        const uint32_t p_t_lo0 = ((smem_u32(sm.p[0][0]) & 0x3FFFFu) >> 4) | kPanelLbo;
+        const uint32_t ds_t_lo0 = ((smem_u32(sm.ds[0][0]) & 0x3FFFFu) >> 4) | kPanelLbo;
+        const uint32_t ds_k_lo0 = smem_desc_sw128_lo(smem_u32(sm.ds[0][0]));
         if (leader) {
             tma_prefetch_desc(&tmap_q);
             tma_prefetch_desc(&tmap_k);
@@ -213,31 +246,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             }
             __syncwarp();
         };
-        int i = next_block(0);
-        if (i < nblk) {  // (a CTA whose keys nobody keeps loads nothing: it only writes zeros to dK_j, dV_j)
-            if (leader) {
-                mbar_arrive_expect_tx_a(a_bar_kv, 2 * kBwdTileBytes);
-                tma_load_3d_a(smem_u32(sm.k), &tmap_k, a_bar_kv, 0, j * kBwdBlock, bh);
-                tma_load_3d_a(smem_u32(sm.v), &tmap_v, a_bar_kv, 0, j * kBwdBlock, bh);
-            }
-            __syncwarp();
-            load_q_do(0, i);
-        }
-        while (i < nblk && ok) {
-            const uint32_t st = steps & 1u;
-            const int i_next = next_block(i + 1);
-            // the other stage was read by the second group of products of the step before
-            if (i_next < nblk) {
-                if (steps >= 1) wait(a_bar_mma2, (steps - 1) & 1u);
-                load_q_do(st ^ 1u, i_next);
-            }
-            wait(a_bar_qdo + 8 * st, (steps >> 1) & 1u);
-            if (steps == 0) wait(a_bar_kv, 0u);
-            // S and dP of the step before have been read: its bar_pds phase was waited for below
+        // S = Q K^T and dP = dO V^T of the query block in stage `st` (contraction over the head dimension: 16 elements =
+        // 32 bytes inside the swizzled 128-byte row)
+        auto issue_s_dp = [&](uint32_t st) {
             tc_fence_after_sync();
             const uint32_t q_lo = smem_desc_sw128_lo(smem_u32(sm.q[st])), do_lo = smem_desc_sw128_lo(smem_u32(sm.dout[st]));
             if (leader && ok) {
-                // contraction over the head dimension: 16 elements = 32 bytes inside the swizzled 128-byte row
 #pragma unroll
                 for (int kk = 0; kk < kBwdDim / 16; ++kk) mma_ss_lh(tmem + kBwdColS, q_lo + 2 * kk, k_lo + 2 * kk, kHi, idesc_s, kk ? 1u : 0u);
 #pragma unroll
@@ -245,8 +259,37 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 mma_commit_a(a_bar_sdp);
             }
             __syncwarp();
-            wait(a_bar_pds, steps & 1u);  // P and dS are in shared memory; the dQ of the step before has been read
+        };
+        int i = next_block(0);
+        if (i < nblk) {
+            load_q_do(0, i);
+            wait(a_bar_qdo, 0u);
+        }
+        wait(a_bar_kv, 0u);  // also in a CTA whose keys nobody keeps (it only writes zeros to dK_j, dV_j): the copy must have landed before the CTA ends
+        if (i < nblk) issue_s_dp(0);
+        // Step s: as soon as the compute warps have turned S and dP of block s into P and dS, the tensor core gets S and
+        // dP of block s+1 (which the compute warps then work on) and, behind them, the three products that consume P
+        // and dS of block s.  P/dS, Q/dO and dQ exist twice, so the products of block s run under the arithmetic of
+        // block s+1.
+        while (i < nblk && ok) {
+            const uint32_t st = steps & 1u;
+            const int i_next = next_block(i + 1);
+            if (i_next < nblk) {
+                // the other Q/dO stage was last read by the dV and dK products of the step before
+                if (steps >= 1) wait(smem_u32(&sm.bar_qdo_free), (steps - 1) & 1u);
+                load_q_do(st ^ 1u, i_next);
+            }
+            if (i_next < nblk) {
+                // S and dP of the next block go to the tensor core as soon as this block's have left tensor memory,
+                // while the compute warps are still busy with the arithmetic on them
+                wait(a_bar_qdo + 8 * (st ^ 1u), ((steps + 1) >> 1) & 1u);
+                wait(a_bar_sfree, steps & 1u);
+                issue_s_dp(st ^ 1u);
+            }
+            wait(a_bar_pds, steps & 1u);
             tc_fence_after_sync();
+            const uint32_t q_lo = smem_desc_sw128_lo(smem_u32(sm.q[st])), do_lo = smem_desc_sw128_lo(smem_u32(sm.dout[st]));
+            const uint32_t p_t_lo = p_t_lo0 + st * kStageUnits, ds_t_lo = ds_t_lo0 + st * kStageUnits, ds_k_lo = ds_k_lo0 + st * kStageUnits;
             if (leader && ok) {
                 const uint32_t acc0 = steps ? 1u : 0u;
                 // contraction over the 128 query rows: 16 rows of 128 bytes = 2048 bytes per step, in both operands
@@ -254,10 +297,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 for (int kk = 0; kk < kBwdBlock / 16; ++kk) mma_ss_lh(tmem + kBwdColDV, p_t_lo + 128 * kk, do_lo + 128 * kk, kHi, idesc_t, kk ? 1u : acc0);
 #pragma unroll
                 for (int kk = 0; kk < kBwdBlock / 16; ++kk) mma_ss_lh(tmem + kBwdColDK, ds_t_lo + 128 * kk, q_lo + 128 * kk, kHi, idesc_t, kk ? 1u : acc0);
+                mma_commit_a(smem_u32(&sm.bar_qdo_free));  // (the dQ product below reads neither Q nor dO)
                 // contraction over the 128 keys: dS is K-major, 64 keys per panel; K_j rows are keys
 #pragma unroll
                 for (int kk = 0; kk < kBwdBlock / 16; ++kk)
-                    mma_ss_lh(tmem + kBwdColDQ, ds_k_lo + (kk >> 2) * (kBwdPanelBytes >> 4) + 2 * (kk & 3), k_lo + 128 * kk, kHi, idesc_q, kk ? 1u : 0u);
+                    mma_ss_lh(tmem + kBwdColDQ + 64 * st, ds_k_lo + (kk >> 2) * (kBwdPanelBytes >> 4) + 2 * (kk & 3), k_lo + 128 * kk, kHi, idesc_q,
+                              kk ? 1u : 0u);
                 mma_commit_a(a_bar_mma2);
             }
             __syncwarp();
@@ -272,53 +317,103 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         const uint32_t half = threadIdx.x >> 7;
         const uint32_t tmem_lane = tmem + (static_cast<uint32_t>(32 * (warp & 3)) << 16);
         const float scale_log2e = args.scale * 1.4426950408889634f;
-        const uint32_t a_p = smem_u32(sm.p[half]) + static_cast<uint32_t>(t) * 128u;
-        const uint32_t a_ds = smem_u32(sm.ds[half]) + static_cast<uint32_t>(t) * 128u;
+        const uint32_t a_p0 = smem_u32(sm.p[0][half]) + static_cast<uint32_t>(t) * 128u;
+        const uint32_t a_ds0 = smem_u32(sm.ds[0][half]) + static_cast<uint32_t>(t) * 128u;
         const uint32_t sw = static_cast<uint32_t>(t) & 7u;
-        int prev_row = 0;
-        // dQ of a finished step: tensor memory -> fp32 accumulator in global memory
-        auto flush_dq = [&](uint32_t step, int row) {
+        int prev_row0 = 0;
+        // dQ of a finished step leaves through shared memory and one TMA reduction per half (fp32 add into the
+        // accumulator in global memory).  Per-thread atomics (8 vector atomics per thread and step) filled the
+        // load/store queue that the control warp's barrier and shared-memory accesses also go through, and held it up
+        // for as long as they took.  The staging tile is the P panel of the finished step, free once its products are
+        // complete: [128 rows][32 fp32 = 128 bytes], 128-byte swizzle, this half's columns.
+        const bool reducer = (threadIdx.x & 127u) == 0;  // the thread of a half that issues its reductions
+        const uint32_t a_bar_half = smem_u32(&sm.bar_half[half]);
+        uint32_t half_phase = 0;
+        // the 128 threads of the half meet (a bounded wait: a thread that gave up elsewhere holds nobody for ever)
+        auto half_sync = [&]() {
+            mbar_arrive_a(a_bar_half);
+            wait(a_bar_half, half_phase & 1u);
+            ++half_phase;
+        };
+        auto read_dq = [&](uint32_t step, float (&dq)[32]) {
             wait(a_bar_mma2, step & 1u);
             tc_fence_after_sync();
             if (!ok) return;
-            float dq[32];
-            tmem_ld32_f32(tmem_lane + kBwdColDQ + 32 * half, dq);
+            tmem_ld32_f32(tmem_lane + kBwdColDQ + 64 * (step & 1u) + 32 * half, dq);
             tmem_wait_ld();
-            if (row < N) {
-                float4* dst = reinterpret_cast<float4*>(args.dq_accum + (static_cast<size_t>(bh) * N + row) * kBwdDim + 32 * half);
+        };
+        auto reduce_dq = [&](uint32_t step, const float (&dq)[32], int row0) {
+            const uint32_t a_stage = smem_u32(sm.p[step & 1u][half]);
+            const uint32_t a_row = a_stage + static_cast<uint32_t>(t) * 128u;
 #pragma unroll
-                for (int c = 0; c < 8; ++c) atomicAdd(dst + c, make_float4(dq[4 * c], dq[4 * c + 1], dq[4 * c + 2], dq[4 * c + 3]));
+            for (int g = 0; g < 8; ++g)
+                sts_v4(a_row + ((static_cast<uint32_t>(g) ^ sw) << 4),
+                       make_uint4(__float_as_uint(dq[4 * g]), __float_as_uint(dq[4 * g + 1]), __float_as_uint(dq[4 * g + 2]),
+                                  __float_as_uint(dq[4 * g + 3])));
+            fence_proxy_async_smem();
+            half_sync();
+            if (reducer && ok) {
+                tma_reduce_add_3d(&tmap_dq, a_stage, 32 * static_cast<int>(half), row0, bh);
+                tma_store_commit();
             }
         };
-        int i = next_block(0);
-        while (i < nblk && ok) {
-            const int row = i * kBwdBlock + t;
-            uint32_t mw[2] = {0u, 0u};
-            float neg_lse_l2 = 0.f, delta = 0.f;
-            if (row < N) {
-                const float lse = args.lse[static_cast<size_t>(bh) * N + row];
-                delta = args.delta[static_cast<size_t>(bh) * N + row];
-                if (lse != -INFINITY) {  // a row that keeps nothing has P = 0 everywhere
-                    neg_lse_l2 = -lse * 1.4426950408889634f;
-#pragma unroll
-                    for (int w = 0; w < 2; ++w) {
-                        const int wi = 4 * j + 2 * static_cast<int>(half) + w;
-                        if (wi < nw) mw[w] = ldg_u32(mask_bh + static_cast<size_t>(row) * nw + wi);
-                    }
-                }
+        // before the half writes a P panel again: the reduction that used it as its staging tile has read it
+        auto staging_free = [&]() {
+            if (reducer) tma_store_wait_read();
+            half_sync();
+        };
+        // this thread's inputs for a block of query rows: log-sum-exp and delta of its row, its two mask words.  Requested
+        // one block ahead, so that the loads' latency lies under the block in work.
+        struct RowIn {
+            float lse, delta;
+            uint32_t mw0, mw1;
+        };
+        auto load_row = [&](int blk) {
+            RowIn r{0.f, 0.f, 0u, 0u};
+            const int row = blk * kBwdBlock + t;
+            if (blk < nblk && row < N) {
+                r.lse = args.lse[static_cast<size_t>(bh) * N + row];
+                r.delta = args.delta[static_cast<size_t>(bh) * N + row];
+                const int wi = 4 * j + 2 * static_cast<int>(half);
+                const uint32_t* mrow = mask_bh + static_cast<size_t>(row) * nw;
+                if (wi < nw) r.mw0 = mrow[wi];
+                if (wi + 1 < nw) r.mw1 = mrow[wi + 1];
+            } else {
+                r.lse = -INFINITY;  // rows past the end keep nothing
             }
-            // the products of the step before read P and dS from shared memory and wrote dQ: both must be over; the
-            // atomics of its dQ run while the tensor core works on this step's S and dP
-            if (steps >= 1) flush_dq(steps - 1, prev_row);
+            return r;
+        };
+        int i = next_block(0);
+        RowIn in_next = load_row(i);
+        while (i < nblk && ok) {
+            const RowIn in = in_next;
+            const int i_next = next_block(i + 1);
+            in_next = load_row(i_next);
+            uint32_t mw[2] = {in.mw0, in.mw1};
+            float neg_lse_l2 = 0.f;
+            const float delta = in.delta;
+            if (in.lse != -INFINITY) {
+                neg_lse_l2 = -in.lse * 1.4426950408889634f;
+            } else {  // a row that keeps nothing has P = 0 everywhere
+                mw[0] = mw[1] = 0u;
+            }
             wait(a_bar_sdp, steps & 1u);
             tc_fence_after_sync();
             if (!ok) break;
+            // this step's P/dS buffer was last read by the products of the step before last: complete, because this
+            // thread waited for them before it arrived for the step before (below)
+            const uint32_t a_p = a_p0 + (steps & 1u) * 2 * kBwdPanelBytes, a_ds = a_ds0 + (steps & 1u) * 2 * kBwdPanelBytes;
+            if (steps >= 2) staging_free();  // the dQ of the step before last went out through this P panel
 #pragma unroll
             for (int c = 0; c < 2; ++c) {  // 32 keys at a time
                 float s[32], dp[32];
                 tmem_ld32_f32(tmem_lane + kBwdColS + 64 * half + 32 * c, s);
                 tmem_ld32_f32(tmem_lane + kBwdColDP + 64 * half + 32 * c, dp);
                 tmem_wait_ld();
+                if (c == 1) {  // this thread's part of S and dP is in registers: the tensor core may overwrite it
+                    tc_fence_before_sync();
+                    mbar_arrive_a(a_bar_sfree);
+                }
                 const uint32_t bits = mw[c];
                 uint32_t pw[16], dw[16];
 #pragma unroll
@@ -339,13 +434,24 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 }
             }
             fence_proxy_async_smem();
+            // dQ of the step before (its products ran under this step's arithmetic) leaves tensor memory before this
+            // thread arrives: the products of this step, issued behind the arrival, write the other dQ buffer, and the
+            // ones after them this one
+            float dq[32];
+            if (steps >= 1) read_dq(steps - 1, dq);
             tc_fence_before_sync();
             mbar_arrive_a(a_bar_pds);
-            prev_row = row;
+            if (steps >= 1 && ok) reduce_dq(steps - 1, dq, prev_row0);
+            prev_row0 = i * kBwdBlock;
             ++steps;
-            i = next_block(i + 1);
+            i = i_next;
         }
-        if (steps >= 1 && ok) flush_dq(steps - 1, prev_row);
+        if (steps >= 1 && ok) {
+            float dq[32];
+            read_dq(steps - 1, dq);
+            if (ok) reduce_dq(steps - 1, dq, prev_row0);
+        }
+        if (reducer) tma_store_wait_all();  // the reductions are complete before the CTA (and its shared memory) goes
         // ---- dK_j (warps 0-3) and dV_j (warps 4-7): tensor-memory lane t is key 128 j + t ----
         const int key = j * kBwdBlock + t;
         if (ok) {

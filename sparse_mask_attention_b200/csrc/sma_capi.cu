@@ -138,6 +138,37 @@ int make_qkv_tensor_map(CUtensorMap* map, const void* base, int BH, int N, int b
     return SMA_OK;
 }
 
+// Tensor map over the backward pass's fp32 dQ accumulator [BH, N, 64]; one box = 128 rows x 32 columns (128 bytes),
+// 128-byte swizzle: the tile one half of the backward kernel's compute warps adds to it per step.
+int make_dq_accum_tensor_map(CUtensorMap* map, const float* base, int BH, int N) {
+    const TensorMapKey key = {base, BH, N, 5000};
+    TensorMapSlot& slot = tensor_map_slot(key);
+    if (slot.key == key) {
+        *map = slot.map;
+        return SMA_OK;
+    }
+    EncodeTiledFn encode = encode_tiled_fn();
+    if (!encode) return SMA_ERR_CUDA;
+    const cuuint64_t dims[3] = {64, static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(BH)};
+    const cuuint64_t strides[2] = {256, static_cast<cuuint64_t>(N) * 256};
+    const cuuint32_t box[3] = {32, 128, 1};
+    const cuuint32_t elem_strides[3] = {1, 1, 1};
+    auto encode_once = [&]() {
+        return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, elem_strides,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    };
+    CUresult r = encode_once();
+    if (r == CUDA_ERROR_INVALID_CONTEXT && bind_primary_context()) r = encode_once();
+    if (r != CUDA_SUCCESS) {
+        tls_cuda_error = static_cast<int>(cudaErrorInvalidValue);
+        return SMA_ERR_CUDA;
+    }
+    slot.key = key;
+    slot.map = *map;
+    return SMA_OK;
+}
+
 // Whether the packed mask [BH, N, nw] can be described by a tensor map: 16-byte aligned base and row pitch.
 bool mask_has_tensor_map(const uint32_t* base, int N) {
     const int nw = (N + 31) / 32;
@@ -240,7 +271,7 @@ int launch_attention(DeviceInfo* dev, int slot, const CUtensorMap& tq, const CUt
 
 template <bool kBf16>
 static int launch_backward(DeviceInfo* dev, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                           const CUtensorMap& tdo, const sma::BwdArgs& args, const void* dout, const void* out, void* dq,
+                           const CUtensorMap& tdo, const CUtensorMap& tdq, const sma::BwdArgs& args, const void* dout, const void* out, void* dq,
                            cudaStream_t stream) {
     const size_t rows = static_cast<size_t>(args.BH) * args.N;
     {
@@ -265,7 +296,7 @@ static int launch_backward(DeviceInfo* dev, const CUtensorMap& tq, const CUtenso
         }
     }
     const unsigned blocks = static_cast<unsigned>(static_cast<long long>(args.BH) * ((args.N + sma::kBwdBlock - 1) / sma::kBwdBlock));
-    if (!cuda_ok(launch_plain(kernel, blocks, sma::kBwdThreads, smem, stream, tq, tk, tv, tdo, args))) return SMA_ERR_CUDA;
+    if (!cuda_ok(launch_plain(kernel, blocks, sma::kBwdThreads, smem, stream, tq, tk, tv, tdo, tdq, args))) return SMA_ERR_CUDA;
     {
         const size_t n2 = rows * sma::kBwdDim / 2;
         size_t blocks2 = (n2 + 255) / 256;
@@ -562,8 +593,10 @@ int sma_attention_bwd(const sma_attention_params* p, const void* dout, void* dq,
     args.BH = static_cast<int32_t>(BH);
     args.N = p->N;
     args.scale = p->scale;
-    return bf16 ? launch_backward<true>(dev, tq, tk, tv, tdo, args, dout, p->out, dq, stream)
-                : launch_backward<false>(dev, tq, tk, tv, tdo, args, dout, p->out, dq, stream);
+    CUtensorMap tdq;
+    if (int st = make_dq_accum_tensor_map(&tdq, args.dq_accum, static_cast<int>(BH), p->N)) return st;
+    return bf16 ? launch_backward<true>(dev, tq, tk, tv, tdo, tdq, args, dout, p->out, dq, stream)
+                : launch_backward<false>(dev, tq, tk, tv, tdo, tdq, args, dout, p->out, dq, stream);
 }
 
 // ---- the entry point that allocates nothing -----------------------------------------------------------------

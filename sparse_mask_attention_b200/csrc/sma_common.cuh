@@ -221,6 +221,15 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* tmap, const void
                  "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2)
                  : "memory");
 }
+// TMA reduction shared -> global: every element of the tile is added to the element of the tensor it maps to (the
+// element type comes from the tensor map; rows outside the tensor are clipped), tracked by bulk groups.
+__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* tmap, uint32_t smem_src, int32_t c0, int32_t c1,
+                                                  int32_t c2) {
+    asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                     reinterpret_cast<uint64_t>(tmap)),
+                 "r"(smem_src), "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // All bulk groups of this thread have finished reading their shared-memory source.
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
