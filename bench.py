@@ -21,7 +21,7 @@ roofline   the attention kernel: skip-adjusted flops per launch / mean launch ti
            bf16 tensor peak; the launch times come from a separate pass over K steps with CUDA events
            around every launch (the timed regions themselves carry no events between their kernels)
 other_configs   the block-sparse and the causal bf16 configuration and the keep-probability sweep, a few steps each
-comparators     the reference project's own CUDA kernels (recompiled for sm_100a) and torch's fused attention on
+comparators     the reference project's own CUDA kernels (recompiled for sm_100a), torch's fused attention and flash-attn on
                 the same inputs, launches back to back, outside every timed region
 cpu_baseline / --impl reference: the reference's CPU path (PyTorch masked attention on the host cores)
 """
@@ -518,6 +518,25 @@ def main():
                                                "what": "the reference's cuDNN adapter (run.py:508-525): SDPA pinned to SDPBackend.CUDNN_ATTENTION"}
         except Exception as e:
             comparators["torch_sdpa_cudnn"] = {"error": repr(e)[:200]}
+
+        try:
+            from flash_attn import flash_attn_func
+
+            # the reference's adapter (run.py:587-606): dense attention WITHOUT the mask, as a no-mask baseline; it
+            # times the layout change to [B, N, H, D] with the kernel, so this does too
+            def fa(i):
+                qf, kf, vf = (t.permute(0, 2, 1, 3).contiguous() for t in (q0, k0, v0))
+                return flash_attn_func(qf, kf, vf, dropout_p=0.0, softmax_scale=None, causal=False).permute(0, 2, 1, 3)
+
+            f_ms = alone_ms(fa, 10)
+            qf, kf, vf = (t.permute(0, 2, 1, 3).contiguous() for t in (q0, k0, v0))
+            k_ms = alone_ms(lambda i: flash_attn_func(qf, kf, vf, dropout_p=0.0, softmax_scale=None, causal=False), 10)
+            comparators["flash_attn_dense_no_mask"] = {
+                "attention_us": f_ms * 1e3, "kernel_only_us": k_ms * 1e3,
+                "what": "the reference's flash-attn adapter (run.py:587-606): flash_attn_func on all keys, mask ignored, "
+                        "layout change included; kernel_only_us without the layout change"}
+        except Exception as e:
+            comparators["flash_attn_dense_no_mask"] = {"error": repr(e)[:200]}
 
     # ---- max over ranks, and the per-rank figures ------------------------------------------------------
     mine = torch.tensor([median_region_ms, e2e_ms, statistics.mean(attn_ms), statistics.mean(pack_ms), attn_alone_ms,
