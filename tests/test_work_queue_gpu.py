@@ -55,15 +55,17 @@ def test_queue_and_fixed_assignment_agree_bitwise(B, H, N, kind, keep, dtype):
         gu.assert_lse_close(results[1][1].cpu().numpy(), ref_lse, "work queue %s N=%d" % (kind, N))
 
 
-def test_python_layer_results_unchanged():
-    cfg = workloads.CONFIGS[3]
+@pytest.mark.parametrize("cfg", [workloads.CONFIGS[3],
+                                 workloads.Config("long", 1, 6, 2112, torch.float16, "block", 0.1, seed=4),
+                                 workloads.Config("long_bf16", 1, 4, 4096, torch.bfloat16, "causal_iid", 0.5, seed=5)])
+def test_python_layer_results_unchanged(cfg):
     q, k, v, mask = (t.cuda() for t in workloads.make_inputs(cfg))
     from sparse_mask_attention_b200.sparse_attention import sparse_attention_func
 
-    out = sparse_attention_func(q, k, v, mask)  # takes the queue
+    out = sparse_attention_func(q, k, v, mask)  # takes the queue (and, beyond 2048 keys, the occupancy side-band)
     packed = sparse_attn_cuda.pack_mask(mask)
     out2 = torch.empty_like(q)
-    sparse_attn_cuda.forward(q, k, v, packed, out2, None, 0.125, False)  # fixed assignment
+    sparse_attn_cuda.forward(q, k, v, packed, out2, None, 0.125, False)  # fixed assignment (tile-list kernel when long)
     torch.cuda.synchronize()
     _capi.device_status()
     assert torch.equal(out, out2)
