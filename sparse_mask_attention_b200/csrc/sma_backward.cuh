@@ -11,7 +11,8 @@
 //
 // Three kernels:
 //   bwd_prepare_kernel  delta = rowsum(dO o O) in fp32 and zeroes of the fp32 dQ accumulator (one warp per row)
-//   attn_bwd_kernel     one CTA per (batch*head, block of 128 keys).  It keeps K_j and V_j in shared memory, walks
+//   attn_bwd_kernel     persistent CTAs, one per SM, that share out units of work = (batch*head, block of 128 keys)
+//                       through a queue.  For a unit the CTA keeps K_j and V_j in shared memory, walks
 //                       the blocks of 128 query rows that keep anything in its 128 keys, and per such block issues
 //                       five tcgen05 products: S = Q K^T and dP = dO V^T into tensor memory; eight warps (two
 //                       threads per query row, 64 keys each) turn them into P and dS, written as 16-bit tiles into
@@ -69,7 +70,8 @@ struct BwdSmem {
     uint64_t bar_qdo_free;  // tensor core: the products that read the step's Q and dO tiles (dV, dK) are complete
     uint32_t tmem_base;
     uint32_t abort_flag;
-    uint32_t qblock_any[kBwdMaxQBlocks / 32];  // bit i: query block i keeps something in this CTA's keys
+    uint32_t next_unit;     // the unit this CTA takes after the one in work
+    uint32_t qblock_any[kBwdMaxQBlocks / 32];  // bit i: query block i keeps something in the keys of the unit in work
 };
 
 constexpr size_t bwd_smem_bytes() { return sizeof(BwdSmem) + 1024; }
@@ -84,14 +86,19 @@ struct BwdArgs {
     int32_t BH;
     int32_t N;
     float scale;
+    // Work queue of the persistent CTAs (units = (key block, batch*head) pairs), or nullptr: a 32-bit word that
+    // bwd_prepare_kernel, the kernel before this one in the stream, has set to zero.  A CTA's first unit is its own
+    // index; every further one comes from the queue (without it: index + k * grid).
+    uint32_t* unit_counter;
 };
 
 // delta[row] = sum_d dout[row, d] * out[row, d]; dq_accum[row, :] = 0.  One warp per row of 64 values.
 template <bool kBf16>
 __global__ void __launch_bounds__(256)
 bwd_prepare_kernel(const uint32_t* __restrict__ dout, const uint32_t* __restrict__ out, float* __restrict__ delta,
-                   float* __restrict__ dq_accum, size_t rows) {
+                   float* __restrict__ dq_accum, size_t rows, uint32_t* __restrict__ unit_counter) {
     const int lane = threadIdx.x & 31;
+    if (unit_counter != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *unit_counter = 0u;  // attn_bwd_kernel's work queue
     const size_t warps = static_cast<size_t>(gridDim.x) * (blockDim.x >> 5);
     for (size_t row = static_cast<size_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows; row += warps) {
         const uint32_t a = dout[row * 32 + lane], b = out[row * 32 + lane];  // two 16-bit values each
@@ -134,8 +141,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const int N = args.N;
     const int nw = (N + 31) >> 5;
     const int nblk = (N + kBwdBlock - 1) / kBwdBlock;  // key blocks == query blocks
-    const int j = static_cast<int>(blockIdx.x % nblk);  // this CTA's key block
-    const int bh = static_cast<int>(blockIdx.x / nblk);
+    // A unit of work = (key block j, batch*head bh); unit u = j * BH + bh, so that for causal-like masks, whose early
+    // key blocks are kept by the most query blocks, the long units come first.  CTAs are persistent.
+    const long long units = static_cast<long long>(args.BH) * nblk;
+    int j = 0, bh = 0;                      // of the unit in work
+    const uint32_t* mask_bh = nullptr;
+    uint32_t g = 0;                         // steps (query blocks walked) over all units of this CTA: barrier phases
+    uint32_t unit_no = 0;                   // units done by this CTA
     constexpr uint32_t kFmt = kBf16 ? kFmtBF16 : kFmtF16;
     volatile uint32_t* abort_flag = &sm.abort_flag;
 
@@ -151,7 +163,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         mbar_init(&sm.bar_half[0], 128);
         mbar_init(&sm.bar_half[1], 128);
         sm.abort_flag = 0u;
-        for (int i = 0; i < kBwdMaxQBlocks / 32; ++i) sm.qblock_any[i] = 0u;
         mbar_init_fence();
     }
     __syncwarp();
@@ -163,45 +174,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = sm.tmem_base;
-
-    // ---- which query blocks keep anything in keys 128j..128j+127: thread t looks at row t of every block ----
-    const uint32_t* mask_bh = args.mask_packed + static_cast<size_t>(bh) * N * nw;
-    // Plain loads (this kernel is launched the ordinary way: everything written before it is visible), and all loads of
-    // a batch of four blocks before the first ballot: the shared-memory atomic below keeps the compiler from moving
-    // later loads above it, and one block at a time the scan paid a full memory latency per block.
-    if (warp < kBwdComputeWarps) {
-        const int trow = static_cast<int>(threadIdx.x & 127u);
-        for (int i0 = warp >> 2; i0 < nblk; i0 += 8) {  // warps 0-3 take the even blocks, warps 4-7 the odd ones
-            uint32_t any[4];
-#pragma unroll
-            for (int b = 0; b < 4; ++b) {
-                const int i = i0 + 2 * b, row = i * kBwdBlock + trow;
-                any[b] = 0u;
-                if (i < nblk && row < N) {
-                    const uint32_t* mrow = mask_bh + static_cast<size_t>(row) * nw + 4 * j;
-#pragma unroll
-                    for (int w = 0; w < 4; ++w)
-                        if (4 * j + w < nw) any[b] |= mrow[w];
-                }
-            }
-#pragma unroll
-            for (int b = 0; b < 4; ++b) {
-                const int i = i0 + 2 * b;
-                const uint32_t some = __ballot_sync(0xFFFFFFFFu, any[b] != 0u);
-                if (lane == 0 && some != 0u) atomicOr(&sm.qblock_any[i >> 5], 1u << (i & 31));
-            }
-        }
-    } else {
-        // meanwhile the control warp asks for K_j and V_j, which every CTA with work needs whatever the scan finds
-        if (lane == 0) {
-            const uint32_t bar = smem_u32(&sm.bar_kv);
-            mbar_arrive_expect_tx_a(bar, 2 * kBwdTileBytes);
-            tma_load_3d_a(smem_u32(sm.k), &tmap_k, bar, 0, j * kBwdBlock, bh);
-            tma_load_3d_a(smem_u32(sm.v), &tmap_v, bar, 0, j * kBwdBlock, bh);
-        }
-        __syncwarp();
-    }
-    __syncthreads();
 
     const uint32_t a_bar_kv = smem_u32(&sm.bar_kv), a_bar_qdo = smem_u32(&sm.bar_qdo[0]), a_bar_sdp = smem_u32(&sm.bar_sdp),
                    a_bar_pds = smem_u32(&sm.bar_pds), a_bar_mma2 = smem_u32(&sm.bar_mma2), a_bar_sfree = smem_u32(&sm.bar_sfree);
@@ -215,7 +187,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         return i;
     };
 
-    uint32_t steps = 0;  // query blocks walked
+    auto begin_unit = [&](long long u) {
+        j = static_cast<int>(u / args.BH);
+        bh = static_cast<int>(u % args.BH);
+        mask_bh = args.mask_packed + static_cast<size_t>(bh) * N * nw;
+    };
     if (warp == kBwdComputeWarps) {
         // ===================================== loads and tensor-core issue =====================================
         // all lanes run the control flow (operands stay in uniform registers); one elected lane issues
@@ -260,54 +236,75 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             }
             __syncwarp();
         };
-        int i = next_block(0);
-        if (i < nblk) {
-            load_q_do(0, i);
-            wait(a_bar_qdo, 0u);
-        }
-        wait(a_bar_kv, 0u);  // also in a CTA whose keys nobody keeps (it only writes zeros to dK_j, dV_j): the copy must have landed before the CTA ends
-        if (i < nblk) issue_s_dp(0);
-        // Step s: as soon as the compute warps have turned S and dP of block s into P and dS, the tensor core gets S and
-        // dP of block s+1 (which the compute warps then work on) and, behind them, the three products that consume P
-        // and dS of block s.  P/dS, Q/dO and dQ exist twice, so the products of block s run under the arithmetic of
-        // block s+1.
-        while (i < nblk && ok) {
-            const uint32_t st = steps & 1u;
-            const int i_next = next_block(i + 1);
-            if (i_next < nblk) {
-                // the other Q/dO stage was last read by the dV and dK products of the step before
-                if (steps >= 1) wait(smem_u32(&sm.bar_qdo_free), (steps - 1) & 1u);
-                load_q_do(st ^ 1u, i_next);
-            }
-            if (i_next < nblk) {
-                // S and dP of the next block go to the tensor core as soon as this block's have left tensor memory,
-                // while the compute warps are still busy with the arithmetic on them
-                wait(a_bar_qdo + 8 * (st ^ 1u), ((steps + 1) >> 1) & 1u);
-                wait(a_bar_sfree, steps & 1u);
-                issue_s_dp(st ^ 1u);
-            }
-            wait(a_bar_pds, steps & 1u);
-            tc_fence_after_sync();
-            const uint32_t q_lo = smem_desc_sw128_lo(smem_u32(sm.q[st])), do_lo = smem_desc_sw128_lo(smem_u32(sm.dout[st]));
-            const uint32_t p_t_lo = p_t_lo0 + st * kStageUnits, ds_t_lo = ds_t_lo0 + st * kStageUnits, ds_k_lo = ds_k_lo0 + st * kStageUnits;
-            if (leader && ok) {
-                const uint32_t acc0 = steps ? 1u : 0u;
-                // contraction over the 128 query rows: 16 rows of 128 bytes = 2048 bytes per step, in both operands
-#pragma unroll
-                for (int kk = 0; kk < kBwdBlock / 16; ++kk) mma_ss_lh(tmem + kBwdColDV, p_t_lo + 128 * kk, do_lo + 128 * kk, kHi, idesc_t, kk ? 1u : acc0);
-#pragma unroll
-                for (int kk = 0; kk < kBwdBlock / 16; ++kk) mma_ss_lh(tmem + kBwdColDK, ds_t_lo + 128 * kk, q_lo + 128 * kk, kHi, idesc_t, kk ? 1u : acc0);
-                mma_commit_a(smem_u32(&sm.bar_qdo_free));  // (the dQ product below reads neither Q nor dO)
-                // contraction over the 128 keys: dS is K-major, 64 keys per panel; K_j rows are keys
-#pragma unroll
-                for (int kk = 0; kk < kBwdBlock / 16; ++kk)
-                    mma_ss_lh(tmem + kBwdColDQ + 64 * st, ds_k_lo + (kk >> 2) * (kBwdPanelBytes >> 4) + 2 * (kk & 3), k_lo + 128 * kk, kHi, idesc_q,
-                              kk ? 1u : 0u);
-                mma_commit_a(a_bar_mma2);
+        for (long long u = blockIdx.x; u < units;) {
+            begin_unit(u);
+            __syncthreads();  // the unit before is over for every thread; its query-block flags have been cleared
+            if (*abort_flag) break;
+            // K_j and V_j, which the unit needs whatever the scan finds, and the unit after this one
+            if (leader) {
+                mbar_arrive_expect_tx_a(a_bar_kv, 2 * kBwdTileBytes);
+                tma_load_3d_a(smem_u32(sm.k), &tmap_k, a_bar_kv, 0, j * kBwdBlock, bh);
+                tma_load_3d_a(smem_u32(sm.v), &tmap_v, a_bar_kv, 0, j * kBwdBlock, bh);
+                const long long next = args.unit_counter != nullptr
+                                           ? static_cast<long long>(gridDim.x) + atomicAdd(args.unit_counter, 1u)
+                                           : u + gridDim.x;
+                sm.next_unit = static_cast<uint32_t>(next < units ? next : units);
             }
             __syncwarp();
-            ++steps;
-            i = i_next;
+            __syncthreads();  // the compute warps have scanned the unit's column strip of the mask
+            const long long u_next = sm.next_unit;
+            uint32_t s = 0;  // steps of this unit
+            int i = next_block(0);
+            if (i < nblk) {
+                load_q_do(g & 1u, i);
+                wait(a_bar_qdo + 8 * (g & 1u), (g >> 1) & 1u);
+            }
+            wait(a_bar_kv, unit_no & 1u);  // also in a unit whose keys nobody keeps: the copy lands before the buffers are reused
+            if (i < nblk) issue_s_dp(g & 1u);
+            // Step: as soon as the compute warps have turned S and dP of a block into P and dS, the tensor core gets S
+            // and dP of the next block (which the compute warps then work on) and, behind them, the three products
+            // that consume P and dS of this one.  P/dS, Q/dO and dQ exist twice, so the products of a block run under
+            // the arithmetic of the next.
+            while (i < nblk && ok) {
+                const uint32_t st = g & 1u;
+                const int i_next = next_block(i + 1);
+                if (i_next < nblk) {
+                    // the other Q/dO stage was last read by the dV and dK products of the step before (at a unit's first
+                    // step: of the unit before, long complete)
+                    if (s >= 1) wait(smem_u32(&sm.bar_qdo_free), (g - 1) & 1u);
+                    load_q_do(st ^ 1u, i_next);
+                    // S and dP of the next block go to the tensor core as soon as this block's have left tensor memory,
+                    // while the compute warps are still busy with the arithmetic on them
+                    wait(a_bar_qdo + 8 * (st ^ 1u), ((g + 1) >> 1) & 1u);
+                    wait(a_bar_sfree, g & 1u);
+                    issue_s_dp(st ^ 1u);
+                }
+                wait(a_bar_pds, g & 1u);
+                tc_fence_after_sync();
+                const uint32_t q_lo = smem_desc_sw128_lo(smem_u32(sm.q[st])), do_lo = smem_desc_sw128_lo(smem_u32(sm.dout[st]));
+                const uint32_t p_t_lo = p_t_lo0 + st * kStageUnits, ds_t_lo = ds_t_lo0 + st * kStageUnits, ds_k_lo = ds_k_lo0 + st * kStageUnits;
+                if (leader && ok) {
+                    const uint32_t acc0 = s ? 1u : 0u;
+                    // contraction over the 128 query rows: 16 rows of 128 bytes = 2048 bytes per step, in both operands
+#pragma unroll
+                    for (int kk = 0; kk < kBwdBlock / 16; ++kk) mma_ss_lh(tmem + kBwdColDV, p_t_lo + 128 * kk, do_lo + 128 * kk, kHi, idesc_t, kk ? 1u : acc0);
+#pragma unroll
+                    for (int kk = 0; kk < kBwdBlock / 16; ++kk) mma_ss_lh(tmem + kBwdColDK, ds_t_lo + 128 * kk, q_lo + 128 * kk, kHi, idesc_t, kk ? 1u : acc0);
+                    mma_commit_a(smem_u32(&sm.bar_qdo_free));  // (the dQ product below reads neither Q nor dO)
+                    // contraction over the 128 keys: dS is K-major, 64 keys per panel; K_j rows are keys
+#pragma unroll
+                    for (int kk = 0; kk < kBwdBlock / 16; ++kk)
+                        mma_ss_lh(tmem + kBwdColDQ + 64 * st, ds_k_lo + (kk >> 2) * (kBwdPanelBytes >> 4) + 2 * (kk & 3), k_lo + 128 * kk, kHi,
+                                  idesc_q, kk ? 1u : 0u);
+                    mma_commit_a(a_bar_mma2);
+                }
+                __syncwarp();
+                ++s;
+                ++g;
+                i = i_next;
+            }
+            u = u_next;
+            ++unit_no;
         }
     } else {
         // ================= two threads per query row (64 keys each): P, dS, dQ, and at the end dK, dV =================
@@ -383,6 +380,40 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             }
             return r;
         };
+        const int trow = t;
+        for (long long u = blockIdx.x; u < units;) {
+            begin_unit(u);
+            if (threadIdx.x < kBwdMaxQBlocks / 32) sm.qblock_any[threadIdx.x] = 0u;  // (nobody reads the old flags any more)
+            __syncthreads();  // the unit before is over for every thread; the flags are clear
+            if (*abort_flag) break;
+            // Which query blocks keep anything in keys 128j..128j+127: thread t looks at row t of every block (warps 0-3
+            // the even blocks, warps 4-7 the odd ones).  Plain loads (this kernel is launched the ordinary way: everything
+            // written before it is visible), and all loads of a batch of four blocks before the first ballot: the
+            // shared-memory atomic below keeps the compiler from moving later loads above it, and one block at a time
+            // the scan paid a full memory latency per block.
+            for (int i0 = warp >> 2; i0 < nblk; i0 += 8) {
+                uint32_t any[4];
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    const int ib = i0 + 2 * b, row = ib * kBwdBlock + trow;
+                    any[b] = 0u;
+                    if (ib < nblk && row < N) {
+                        const uint32_t* mrow = mask_bh + static_cast<size_t>(row) * nw + 4 * j;
+#pragma unroll
+                        for (int w = 0; w < 4; ++w)
+                            if (4 * j + w < nw) any[b] |= mrow[w];
+                    }
+                }
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    const int ib = i0 + 2 * b;
+                    const uint32_t some = __ballot_sync(0xFFFFFFFFu, any[b] != 0u);
+                    if (lane == 0 && some != 0u) atomicOr(&sm.qblock_any[ib >> 5], 1u << (ib & 31));
+                }
+            }
+            __syncthreads();  // the flags are complete (and the control warp has named the next unit)
+            const long long u_next = sm.next_unit;
+            uint32_t steps = 0;  // steps of this unit
         int i = next_block(0);
         RowIn in_next = load_row(i);
         while (i < nblk && ok) {
@@ -397,13 +428,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             } else {  // a row that keeps nothing has P = 0 everywhere
                 mw[0] = mw[1] = 0u;
             }
-            wait(a_bar_sdp, steps & 1u);
+            wait(a_bar_sdp, g & 1u);
             tc_fence_after_sync();
             if (!ok) break;
             // this step's P/dS buffer was last read by the products of the step before last: complete, because this
             // thread waited for them before it arrived for the step before (below)
-            const uint32_t a_p = a_p0 + (steps & 1u) * 2 * kBwdPanelBytes, a_ds = a_ds0 + (steps & 1u) * 2 * kBwdPanelBytes;
-            if (steps >= 2) staging_free();  // the dQ of the step before last went out through this P panel
+            const uint32_t a_p = a_p0 + (g & 1u) * 2 * kBwdPanelBytes, a_ds = a_ds0 + (g & 1u) * 2 * kBwdPanelBytes;
+            if (g >= 2) staging_free();  // the dQ of the step before last (of this unit or the one before) went out through this P panel
 #pragma unroll
             for (int c = 0; c < 2; ++c) {  // 32 keys at a time
                 float s[32], dp[32];
@@ -438,20 +469,20 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             // thread arrives: the products of this step, issued behind the arrival, write the other dQ buffer, and the
             // ones after them this one
             float dq[32];
-            if (steps >= 1) read_dq(steps - 1, dq);
+            if (steps >= 1) read_dq(g - 1, dq);
             tc_fence_before_sync();
             mbar_arrive_a(a_bar_pds);
-            if (steps >= 1 && ok) reduce_dq(steps - 1, dq, prev_row0);
+            if (steps >= 1 && ok) reduce_dq(g - 1, dq, prev_row0);
             prev_row0 = i * kBwdBlock;
             ++steps;
+            ++g;
             i = i_next;
         }
         if (steps >= 1 && ok) {
             float dq[32];
-            read_dq(steps - 1, dq);
-            if (ok) reduce_dq(steps - 1, dq, prev_row0);
+            read_dq(g - 1, dq);
+            if (ok) reduce_dq(g - 1, dq, prev_row0);
         }
-        if (reducer) tma_store_wait_all();  // the reductions are complete before the CTA (and its shared memory) goes
         // ---- dK_j (warps 0-3) and dV_j (warps 4-7): tensor-memory lane t is key 128 j + t ----
         const int key = j * kBwdBlock + t;
         if (ok) {
@@ -475,6 +506,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 for (int c = 0; c < kBwdDim / 8; ++c) dst[c] = make_uint4(outw[4 * c], outw[4 * c + 1], outw[4 * c + 2], outw[4 * c + 3]);
             }
         }
+            // (the next unit's first products overwrite dK and dV in tensor memory: they are issued behind two CTA-wide
+            // barriers that this thread reaches after the loads above have completed)
+            tc_fence_before_sync();
+            u = u_next;
+            ++unit_no;
+        }
+        if (reducer) tma_store_wait_all();  // the reductions are complete before the CTA (and its shared memory) goes
     }
 
     // ---- release tensor memory -------------------------------------------------------------------

@@ -281,7 +281,7 @@ static int launch_backward(DeviceInfo* dev, const CUtensorMap& tq, const CUtenso
         if (blocks > cap) blocks = cap;
         if (!cuda_ok(launch_plain(sma::bwd_prepare_kernel<kBf16>, static_cast<unsigned>(blocks), 256, 0, stream,
                                   static_cast<const uint32_t*>(dout), static_cast<const uint32_t*>(out),
-                                  const_cast<float*>(args.delta), args.dq_accum, rows)))
+                                  const_cast<float*>(args.delta), args.dq_accum, rows, args.unit_counter)))
             return SMA_ERR_CUDA;
     }
     auto kernel = sma::attn_bwd_kernel<kBf16>;
@@ -295,7 +295,9 @@ static int launch_backward(DeviceInfo* dev, const CUtensorMap& tq, const CUtenso
             dev->bwd_attr_set[kBf16 ? 1 : 0] = true;
         }
     }
-    const unsigned blocks = static_cast<unsigned>(static_cast<long long>(args.BH) * ((args.N + sma::kBwdBlock - 1) / sma::kBwdBlock));
+    // persistent CTAs, one per SM, that share out the (key block, batch*head) units through a queue
+    const long long units = static_cast<long long>(args.BH) * ((args.N + sma::kBwdBlock - 1) / sma::kBwdBlock);
+    const unsigned blocks = static_cast<unsigned>(units < dev->sm_count ? units : dev->sm_count);
     if (!cuda_ok(launch_plain(kernel, blocks, sma::kBwdThreads, smem, stream, tq, tk, tv, tdo, tdq, args))) return SMA_ERR_CUDA;
     {
         const size_t n2 = rows * sma::kBwdDim / 2;
@@ -542,14 +544,15 @@ int sma_attention_fwd_planned(const sma_attention_params* p, void* workspace, si
 }
 
 // ---- backward pass -------------------------------------------------------------------------------------------
-// Workspace: delta [BH, N] fp32 (rounded up to 256 bytes), then the dQ accumulator [BH, N, 64] fp32.
+// Workspace: delta [BH, N] fp32 (rounded up to 256 bytes), then the dQ accumulator [BH, N, 64] fp32, then 256 bytes
+// whose first word is the backward kernel's work queue.
 static size_t bwd_delta_bytes(long long BH, int N) { return (static_cast<size_t>(BH) * N * sizeof(float) + 255u) & ~size_t(255); }
 
 size_t sma_attention_bwd_workspace_bytes(int32_t B, int32_t H, int32_t N) {
     if (B < 1 || H < 1 || N < 1 || N > SMA_MAX_SEQ_LEN) return 0;
     const long long BH = 1ll * B * H;
     if (BH * ((N + sma::kBwdBlock - 1) / sma::kBwdBlock) > 0x7FFFFFFFll) return 0;
-    return bwd_delta_bytes(BH, N) + static_cast<size_t>(BH) * N * sma::kBwdDim * sizeof(float);
+    return bwd_delta_bytes(BH, N) + static_cast<size_t>(BH) * N * sma::kBwdDim * sizeof(float) + 256;
 }
 
 int sma_attention_bwd(const sma_attention_params* p, const void* dout, void* dq, void* dk, void* dv, void* workspace,
@@ -588,6 +591,8 @@ int sma_attention_bwd(const sma_attention_params* p, const void* dout, void* dq,
     args.lse = p->lse;
     args.delta = static_cast<float*>(workspace);
     args.dq_accum = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + bwd_delta_bytes(BH, p->N));
+    args.unit_counter = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(args.dq_accum) +
+                                                   static_cast<size_t>(BH) * p->N * sma::kBwdDim * sizeof(float));
     args.dk = dk;
     args.dv = dv;
     args.BH = static_cast<int32_t>(BH);

@@ -121,7 +121,7 @@ def test_autograd_function_uses_the_kernels():
 
 
 def test_workspace_and_argument_checks():
-    assert _capi.attention_bwd_workspace_bytes(2, 3, 128) == 2 * 3 * 128 * 4 + 2 * 3 * 128 * 64 * 4
+    assert _capi.attention_bwd_workspace_bytes(2, 3, 128) == 2 * 3 * 128 * 4 + 2 * 3 * 128 * 64 * 4 + 256
     assert _capi.attention_bwd_workspace_bytes(0, 3, 128) == 0
     cfg = workloads.Config("chk", 1, 1, 128, torch.float16, "iid", 0.25, seed=1)
     q, k, v, mask = (t.cuda() for t in workloads.make_inputs(cfg))
