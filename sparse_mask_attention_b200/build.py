@@ -20,7 +20,8 @@ LIB_PATH = os.path.join(PKG_DIR, LIB_NAME)
 WAIT_TEST_LIB_PATH = os.path.join(PKG_DIR, "libsma_b200_waittest.so")
 
 SOURCES = ["sma_capi.cu"]
-HEADERS = ["sma_common.cuh", "sma_pack.cuh", "sma_plan.cuh", "sma_attention.cuh", os.path.join("..", "..", "include", "sma.h")]
+# every header next to the sources, so that a new one cannot be forgotten here
+HEADERS = sorted(f for f in os.listdir(CSRC_DIR) if f.endswith(".cuh")) + [os.path.join("..", "..", "include", "sma.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
