@@ -11,14 +11,15 @@
 // 64-key tiles, sixteen packed-mask words per row) and visits only the tiles that hold at least one kept bit
 // for those rows.  Warp roles:
 //   * loader warp (1 per stream): per chunk it brings the 128 x 16-word strip of packed-mask words into
-//     shared memory (one TMA tile copy; plain loads for shapes a tensor map cannot describe), finds the
-//     non-empty tiles in it (or takes them from a list or from occupancy bits computed ahead, kLists) and publishes a chunk
-//     descriptor; then it issues the TMA loads (128-byte swizzle) of the item's Q tile and of the listed
-//     K/V tile pairs into a three-stage ring, as the P V products release the stages.
-//   * MMA warp (1 per stream): one thread walks the stream's tile sequence, across chunks and work items
-//     without draining, and issues every tcgen05.mma of the stream:
+//     shared memory (one TMA tile copy, requested from inside the K loop of the chunk before; plain loads for
+//     shapes a tensor map cannot describe), finds the non-empty tiles in it (or takes them from a list or from
+//     occupancy bits computed ahead, kLists) and publishes a chunk descriptor.  Tile by tile it then requests K
+//     (TMA, 128-byte swizzle, three-stage ring of its own) as soon as the stage is free, and, once the product
+//     P V of three tiles back has released the tile's S/P buffer and V stage, requests V and issues
 //         S[128x64]  = Q K^T   (operands in shared memory)
-//         O[128x64] += P V     (P from tensor memory, V MN-major from shared memory)
+//     for the tile whose K landed a tile ago.  All lanes run the control flow, one elected lane issues.
+//   * P V warp (1 per stream): walks the chunk descriptors and issues, as the softmax threads publish P,
+//         O[128x64] += P V     (P from tensor memory, V MN-major from shared memory).
 //     S runs two tiles ahead of the softmax threads (three S/P buffers) and Q is double-buffered, so the
 //     first S products of the next item run while the previous item is still being finished; the next item's
 //     first P V waits until the softmax warps have copied the previous item's O out of tensor memory.
@@ -27,11 +28,15 @@
 //     and writes P (16-bit) with tcgen05.st over the columns its S row came from.  At the end of an item it
 //     goes straight on to the first tile of the next item (whose S is ready) and finishes the previous item
 //     behind that tile, when its last P V has long completed: each warp reads its 32 rows of O, normalises,
-//     rounds, stages them in shared memory and stores them with one TMA store.
+//     rounds, stages them in shared memory and stores them with one TMA store.  On dense single-chunk work the
+//     two softmax warps that share a scheduler (one of each stream) take turns at the exponentials.
+// Work items are dealt to the CTAs round-robin, or, when the call provides a counter, taken from a queue shared by
+// all CTAs (AttnArgs::work_counter).
 // Hand-offs are mbarriers (TMA transaction counts, tcgen05.commit, thread arrivals); every wait is bounded.
-// Orderings that need no barrier of their own, because one thread issues all products of a stream and the
-// tensor core runs them in issue order:
-//   * S(j) may overwrite buffer j%3 once P V(j-3) has been issued: that product read the buffer's previous P.
+// Orderings that hold because the tensor core runs a CTA's products in issue order and a buffer's two products come
+// from warps that hand it to one another through those barriers:
+//   * S(j) is issued only after P V(j-3) has completed (its commit is what the loader waits for): that product read
+//     the previous P of buffer j%3 and the previous V of the stage.
 //   * P(j) may overwrite S(j) in place: the softmax threads read S(j) before they write P(j).
 #pragma once
 
