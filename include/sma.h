@@ -20,7 +20,7 @@
 extern "C" {
 #endif
 
-#define SMA_ABI_VERSION 3
+#define SMA_ABI_VERSION 4
 
 typedef enum sma_status {
     SMA_OK                 = 0,
@@ -36,7 +36,8 @@ typedef enum sma_status {
     SMA_ERR_DEVICE_TIMEOUT = -10, /* a kernel gave up on a bounded wait (reported by sma_device_status) */
     SMA_ERR_BAD_VARIANT    = -11, /* unknown value in sma_attention_params.variant                 */
     SMA_ERR_WORKSPACE_TOO_SMALL = -12, /* workspace smaller than sma_attention_workspace_bytes()  */
-    SMA_ERR_STATIC_WORKSPACE_EXCEEDED = -13 /* shape needs more than SMA_STATIC_WORKSPACE_BYTES    */
+    SMA_ERR_STATIC_WORKSPACE_EXCEEDED = -13, /* shape needs more than SMA_STATIC_WORKSPACE_BYTES   */
+    SMA_ERR_BAD_STRIDE     = -14  /* a stride is not a positive multiple of 8 elements, or strides where none are taken */
 } sma_status;
 
 typedef enum sma_dtype {
@@ -83,6 +84,19 @@ typedef struct sma_attention_params {
     int32_t         dtype;     /* sma_dtype                                                  */
     int32_t         save_lse;  /* reference: SparseAttentionParams::is_training              */
     int32_t         variant;   /* SMA_VARIANT_*                                              */
+    /*
+     * Strides of q, k, v and out in ELEMENTS: {batch, head, row}; the 64 values of a row are always contiguous.
+     * All three zero (what a zero-initialised struct gives) = the dense [B, H, N, 64] layout.  Otherwise every stride
+     * must be positive and a multiple of 8 elements (16 bytes): a packed projection [B, N, 3, H, 64] viewed as
+     * q[b, h, n, :] is {3*N*H*64, 64, 3*H*64}, no copy needed.  Reference: SparseAttentionParams::stride_qb ...
+     * stride_on (csrc/sparse_attention.h:29-33), which its kernels never read (its binding copies to the dense layout
+     * first, csrc/binding.cpp:28-33).  mask_packed and lse are always dense.  The forward entry points honour the
+     * strides; sma_attention_bwd takes dense tensors only (SMA_ERR_BAD_STRIDE otherwise).
+     */
+    int64_t         q_strides[3];
+    int64_t         k_strides[3];
+    int64_t         v_strides[3];
+    int64_t         out_strides[3];
 } sma_attention_params;
 
 /* Returns SMA_ABI_VERSION of the loaded library. */

@@ -11,7 +11,7 @@ import os
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG_DIR, "libsma_b200.so")
 
-SMA_ABI_VERSION = 3
+SMA_ABI_VERSION = 4
 SMA_DTYPE_F16 = 0
 SMA_DTYPE_BF16 = 1
 SMA_VARIANT_DEFAULT = 0
@@ -32,6 +32,7 @@ SMA_ERR_DEVICE_TIMEOUT = -10
 SMA_ERR_BAD_VARIANT = -11
 SMA_ERR_WORKSPACE_TOO_SMALL = -12
 SMA_ERR_STATIC_WORKSPACE_EXCEEDED = -13
+SMA_ERR_BAD_STRIDE = -14
 SMA_STATIC_WORKSPACE_BYTES = 1 << 20
 
 # every symbol include/sma.h declares
@@ -80,6 +81,11 @@ class AttentionParams(ctypes.Structure):
         ("dtype", ctypes.c_int32),
         ("save_lse", ctypes.c_int32),
         ("variant", ctypes.c_int32),
+        # element strides {batch, head, row} of q, k, v, out; all zero = the dense [B, H, N, 64] layout
+        ("q_strides", ctypes.c_int64 * 3),
+        ("k_strides", ctypes.c_int64 * 3),
+        ("v_strides", ctypes.c_int64 * 3),
+        ("out_strides", ctypes.c_int64 * 3),
     ]
 
 

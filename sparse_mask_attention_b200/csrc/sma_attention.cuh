@@ -150,9 +150,9 @@ __device__ __noinline__ void rescale_o_row(uint32_t addr, float alpha) {
 // 32 rows.  inv_l == 0 marks a row that keeps nothing: it is written as zeros whatever the accumulator holds.
 // Arrives on bar_o_free once O is in registers.  Kept out of line: it runs once per work item, and the tile
 // loop around its call site is sensitive to the size of its body.
-template <bool kBf16>
+template <bool kBf16, bool kFourD>
 __device__ __noinline__ void finish_rows(uint32_t o_addr, float inv_l, uint32_t a_stage, uint32_t a_bar_o_free,
-                                         const CUtensorMap* tmap_o, int row0, int bh, bool store) {
+                                         const CUtensorMap* tmap_o, int row0, int h, int b, bool store) {
     const int lane = threadIdx.x & 31;
     // the previous store of this warp must have finished reading the staging tile
     if (lane == 0) tma_store_wait_read();
@@ -185,7 +185,11 @@ __device__ __noinline__ void finish_rows(uint32_t o_addr, float inv_l, uint32_t 
     fence_proxy_async_smem();
     __syncwarp();
     if (lane == 0 && store) {
-        tma_store_3d(tmap_o, reinterpret_cast<const void*>(__cvta_shared_to_generic(a_stage)), 0, row0, bh);
+        // (h, b) = (head, batch entry), or (batch*head, unused) with three-dimensional tensor maps
+        if constexpr (kFourD)
+            tma_store_4d(tmap_o, reinterpret_cast<const void*>(__cvta_shared_to_generic(a_stage)), 0, row0, h, b);
+        else
+            tma_store_3d(tmap_o, reinterpret_cast<const void*>(__cvta_shared_to_generic(a_stage)), 0, row0, h);
         tma_store_commit();
     }
 }
@@ -205,6 +209,7 @@ struct AttnArgs {
     uint32_t* work_counter;
     float* lse;
     int32_t BH;
+    int32_t H;           // heads per batch entry (kFourD kernels)
     int32_t N;
     int32_t num_q_tiles;
     float scale_log2e;   // |scale| * log2(e)
@@ -221,8 +226,13 @@ struct AttnArgs {
 // kLists  : where the loader warps take the tile lists from.  kListsFromStrips: they scan every chunk's mask strip.
 //           kListsFromPlan: AttnArgs::plan.  kListsFromBits: AttnArgs::tile_bits.  In the last two, strips of chunks
 //           without a tile are not loaded at all.  (One instantiation each: the kernel is sensitive to its code size.)
+// kFourD  : the tensor maps of q, k, v, out are four-dimensional (64, N, H, B) and tiles are named (row, head, batch
+//           entry), for layouts in which batch*head is not one dimension.  false: three-dimensional (64, N, B*H), tiles
+//           named (row, batch*head), which every layout whose batch stride is H head strides admits (the dense one
+//           among them).  An instantiation of its own: as a run-time switch in the loader warps the second form cost
+//           the dense layout 1-6 % of the launch.
 constexpr int kListsFromStrips = 0, kListsFromPlan = 1, kListsFromBits = 2;
-template <bool kBf16, bool kSplitP, int kLists>
+template <bool kBf16, bool kSplitP, int kLists, bool kFourD>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o,
@@ -307,6 +317,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     // (row block, batch*head) with the later row blocks first: for causal-like masks they hold most work.
     auto item_bh = [&](int item) { return item % BH; };
     auto item_row0 = [&](int item) { return (args.num_q_tiles - 1 - item / BH) * kBlockM; };
+    // q, k, v and out may have any batch, head and row strides; the packed mask, the log-sum-exp and the side-bands
+    // are dense.  (head, batch entry) of a batch*head index for the four-dimensional maps, (batch*head, 0) otherwise.
+    auto split_bh = [&](int bh, int& h, int& b) {
+        b = kFourD ? bh / args.H : 0;
+        h = bh - b * args.H;
+    };
     bool ok = true;  // false once a bounded wait has run out; the same in all lanes of a warp
     volatile uint32_t* const abort_flag = &sm.abort_flag;
     // Bounded wait on an mbarrier phase.  After a failure nothing is waited for any more.  The lanes of a warp
@@ -415,8 +431,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 swait(a_bar_o_full, fin_r & 1u);
                 tc_fence_after_sync();
                 const int row0 = item_row0(fin_item) + wq * static_cast<int>(kStageRowsOut);
-                finish_rows<kBf16>(tmem_lane + kColO, fin_inv_l, a_stage, a_bar_o_free, &tmap_o, row0, item_bh(fin_item),
-                                   row0 < N && ok);
+                int fin_h, fin_b;
+                split_bh(item_bh(fin_item), fin_h, fin_b);
+                finish_rows<kBf16, kFourD>(tmem_lane + kColO, fin_inv_l, a_stage, a_bar_o_free, &tmap_o, row0, fin_h, fin_b,
+                                           row0 < N && ok);
                 fin_on = false;
             };
             for (;;) {
@@ -813,7 +831,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 bool pend_first = false;  // first tile of its item: the item's Q tile must have landed
                 bool pend_last = false;   // last tile of its item: behind it the Q buffer is free again
                 uint32_t pend_r = 0;      // ordinal of its item
-                int pend_t = 0, pend_bh = 0;  // its key tile and batch*head
+                int pend_t = 0, pend_h = 0, pend_b = 0;  // its key tile, head and batch entry
+                int cur_h = 0, cur_b = 0;                // head and batch entry of the item whose tiles are being requested
                 bool pend_first_of_item = false;  // the next tile to be loaded is the first of its item
                 auto issue_s = [&]() {  // V load and S product of the pending tile (S/P buffer and ring stage ss)
                     // buffer and stage are free when P V of their previous tenant (tile js-3) has completed: that product
@@ -823,7 +842,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                     if (leader && ok) {
                         const uint32_t bar = a_bar_v + 8 * ss;
                         mbar_arrive_expect_tx_a(bar, kKVTileBytes);
-                        tma_load_3d_a(v_a0 + ss * kKVTileBytes, &tmap_v, bar, 0, pend_t * kBlockN, pend_bh);
+                        if constexpr (kFourD)
+                            tma_load_4d_a(v_a0 + ss * kKVTileBytes, &tmap_v, bar, 0, pend_t * kBlockN, pend_h, pend_b);
+                        else
+                            tma_load_3d_a(v_a0 + ss * kKVTileBytes, &tmap_v, bar, 0, pend_t * kBlockN, pend_h);
                     }
                     __syncwarp();
                     const uint32_t qb = pend_r & 1u;
@@ -863,10 +885,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                     if (pend && !__all_sync(0xFFFFFFFFu, mbar_test_wait_a(bar, par))) issue_s();
                     wait(bar, par);
                 };
-                // K loads of the tiles listed in `slot` (for item bh), each as soon as its ring stage is free, and behind
+                // K loads of the tiles listed in `slot` (of the item in work: cur_h, cur_b), each as soon as its ring stage is free, and behind
                 // each the V load and the S product of the tile before.  While waiting, the strip of the following chunk
                 // (item_n, c_n) is requested as soon as its slot is free.
-                auto issue_kv = [&](uint32_t slot, uint32_t count, bool last, int bh, bool have_n, int item_n, int c_n) {
+                auto issue_kv = [&](uint32_t slot, uint32_t count, bool last, bool have_n, int item_n, int c_n) {
                     const uint32_t a_entries = a_desc0 + slot * 32u + 8;
                     for (uint32_t i = 0; i < count && ok; ++i) {
                         const int t = static_cast<int>(__shfl_sync(0xFFFFFFFFu, lds_u16(a_entries + 2 * i), 0) & 0xFFu);
@@ -883,7 +905,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                         if (leader && ok) {
                             const uint32_t bar = a_bar_k + 8 * ls;
                             mbar_arrive_expect_tx_a(bar, kKVTileBytes);
-                            tma_load_3d_a(k_a0 + ls * kKVTileBytes, &tmap_k, bar, 0, t * kBlockN, bh);
+                            if constexpr (kFourD)
+                                tma_load_4d_a(k_a0 + ls * kKVTileBytes, &tmap_k, bar, 0, t * kBlockN, cur_h, cur_b);
+                            else
+                                tma_load_3d_a(k_a0 + ls * kKVTileBytes, &tmap_k, bar, 0, t * kBlockN, cur_h);
                         }
                         __syncwarp();
                         if (pend) issue_s();
@@ -892,7 +917,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                         pend_last = last && i + 1 == count;
                         pend_r = r;
                         pend_t = t;
-                        pend_bh = bh;
+                        pend_h = cur_h;
+                        pend_b = cur_b;
                         if (i == 0) pend_first_of_item = false;
                         ++j;
                         if (++ls == kStages) {
@@ -986,19 +1012,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                     const int item = item_next;
                     item_next = take_item();  // taken one item ahead: its first mask strip is requested early
                     const int bh = item_bh(item);
+                    split_bh(bh, cur_h, cur_b);
                     // Q tile into buffer r % 2, last used by item r-2: all its S products must be complete
                     if (r >= 2) wait(a_bar_q_free + 8 * (r & 1u), ((r >> 1) - 1) & 1u);
 #ifdef SMA_WAIT_TEST_BUILD
-                    // test build only: on request, the first Q tile of stream 0 of CTA 0 is never asked for, nothing
-                    // completes its barrier, and this warp's wait for it runs out
-                    const bool withheld = g_test_withhold_q_load != 0 && blockIdx.x == 0 && stream == 0 && r == 0;
+                    // test build only: on request, the Q tile of work item 0 (whichever stream of CTA 0 takes it) is never
+                    // asked for, nothing completes its barrier, and this warp's wait for it runs out
+                    const bool withheld = g_test_withhold_q_load != 0 && item == 0;
 #else
                     constexpr bool withheld = false;
 #endif
                     if (leader && ok && !withheld) {
                         const uint32_t bar = a_bar_q + 8 * (r & 1u);
                         mbar_arrive_expect_tx_a(bar, kQTileBytes);
-                        tma_load_3d_a(q_a0 + (r & 1u) * kQTileBytes, &tmap_q, bar, 0, item_row0(item), bh);
+                        if constexpr (kFourD)
+                            tma_load_4d_a(q_a0 + (r & 1u) * kQTileBytes, &tmap_q, bar, 0, item_row0(item), cur_h, cur_b);
+                        else
+                            tma_load_3d_a(q_a0 + (r & 1u) * kQTileBytes, &tmap_q, bar, 0, item_row0(item), cur_h);
                     }
                     __syncwarp();
                     pend_first_of_item = true;
@@ -1048,7 +1078,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                                 publish(slot, item, __popc(any), last);
                                 // (requesting the next descriptor's strip from inside the K loop, as the strip-scanning
                                 // loader does, was measured here too and gained nothing)
-                                issue_kv(slot, __popc(any), last, bh, false, 0, 0);
+                                issue_kv(slot, __popc(any), last, false, 0, 0);
                                 item_has_tiles = true;
                                 last_marked = last;
                                 ++u;
@@ -1092,7 +1122,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                             pos += count;
                             const bool last = pos >= total;
                             publish(slot, item, count, last);
-                            issue_kv(slot, count, last, bh, false, 0, 0);
+                            issue_kv(slot, count, last, false, 0, 0);
                             item_has_tiles |= count > 0;
                             last_marked = last && count > 0;
                             ++u;
@@ -1117,7 +1147,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                             const bool last = c + 1 == num_chunks;
                             publish(slot, item, count, last);
                             const bool have_n = !last || item_next >= 0;
-                            issue_kv(slot, count, last, bh, have_n, last ? item_next : item, last ? 0 : c + 1);
+                            issue_kv(slot, count, last, have_n, last ? item_next : item, last ? 0 : c + 1);
                             item_has_tiles |= count > 0;
                             last_marked = last && count > 0;
                             ++u;

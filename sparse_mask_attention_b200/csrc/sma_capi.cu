@@ -31,7 +31,7 @@ struct DeviceInfo {
     bool checked = false;
     bool is_sm100 = false;
     int sm_count = 0;
-    bool attn_attr_set[12] = {};
+    bool attn_attr_set[18] = {};
     bool bwd_attr_set[2] = {};
 };
 DeviceInfo g_dev[kMaxDevices];
@@ -91,10 +91,15 @@ struct TensorMapKey {
     int32_t bh;
     int32_t n;
     int32_t kind;  // box rows for q/k/v/out maps (fp16), + 1000 for bf16, -1 for the packed-mask map
-    bool operator==(const TensorMapKey& o) const { return base == o.base && bh == o.bh && n == o.n && kind == o.kind; }
+    int64_t stride[3] = {0, 0, 0};  // element strides {batch, head, row} of the strided maps, zero otherwise
+    int32_t heads = 0;              // heads per batch entry of the strided maps
+    bool operator==(const TensorMapKey& o) const {
+        return base == o.base && bh == o.bh && n == o.n && kind == o.kind && stride[0] == o.stride[0] &&
+               stride[1] == o.stride[1] && stride[2] == o.stride[2] && heads == o.heads;
+    }
 };
 struct TensorMapSlot {
-    TensorMapKey key = {nullptr, 0, 0, 0};
+    TensorMapKey key = {nullptr, 0, 0, 0, {0, 0, 0}, 0};
     CUtensorMap map;
 };
 constexpr int kTensorMapSlots = 64;
@@ -107,8 +112,61 @@ TensorMapSlot& tensor_map_slot(const TensorMapKey& key) {
     return tls_tensor_maps[(h >> 20) % kTensorMapSlots];
 }
 
+// Element strides {batch, head, row} of one of q/k/v/out: the caller's, or those of the dense [B, H, N, 64] layout
+// when all three are zero.  false: not positive multiples of 8 elements.
+bool resolve_strides(const int64_t (&given)[3], int H, int N, int64_t (&out)[3]) {
+    if (given[0] == 0 && given[1] == 0 && given[2] == 0) {
+        out[0] = static_cast<int64_t>(H) * N * 64;
+        out[1] = static_cast<int64_t>(N) * 64;
+        out[2] = 64;
+        return true;
+    }
+    for (int i = 0; i < 3; ++i) {
+        if (given[i] <= 0 || (given[i] & 7) != 0 || given[i] >= (1ll << 38)) return false;
+        out[i] = given[i];
+    }
+    return true;
+}
+
+// Tensor map over a 16-bit tensor addressed as [B][H][N][64] with element strides {batch, head, row}; one box =
+// box_rows x 64 elements of one (batch, head), written to shared memory with the 128-byte swizzle.  Rows past N
+// read as zeros.  four_d: dimensions (64, N, H, B); otherwise (64, N, B*H), for layouts whose batch stride is H head
+// strides.
+int make_strided_tensor_map(CUtensorMap* map, const void* base, int B, int H, int N, const int64_t (&stride)[3],
+                            int box_rows, bool bf16, bool four_d) {
+    TensorMapKey key = {base, B * H, N, (four_d ? 4000 : 2000) + box_rows + (bf16 ? 1000 : 0), {stride[0], stride[1], stride[2]}, H};
+    TensorMapSlot& slot = tensor_map_slot(key);
+    if (slot.key == key) {
+        *map = slot.map;
+        return SMA_OK;
+    }
+    EncodeTiledFn encode = encode_tiled_fn();
+    if (!encode) return SMA_ERR_CUDA;
+    const cuuint64_t dims[4] = {64, static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(four_d ? H : B * H),
+                                static_cast<cuuint64_t>(B)};
+    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(stride[2]) * 2, static_cast<cuuint64_t>(stride[1]) * 2,
+                                   static_cast<cuuint64_t>(stride[0]) * 2};
+    const cuuint32_t box[4] = {64, static_cast<cuuint32_t>(box_rows), 1, 1};
+    const cuuint32_t elem_strides[4] = {1, 1, 1, 1};
+    auto encode_once = [&]() {
+        return encode(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, four_d ? 4 : 3,
+                      const_cast<void*>(base), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    };
+    CUresult r = encode_once();
+    if (r == CUDA_ERROR_INVALID_CONTEXT && bind_primary_context()) r = encode_once();
+    if (r != CUDA_SUCCESS) {
+        tls_cuda_error = static_cast<int>(cudaErrorInvalidValue);
+        return SMA_ERR_CUDA;
+    }
+    slot.key = key;
+    slot.map = *map;
+    return SMA_OK;
+}
+
 // Tensor map over a [BH, N, 64] row-major 16-bit tensor; one box = box_rows x 64 elements of one
 // (batch, head), written to shared memory with the 128-byte swizzle.  Rows past N read as zeros.
+// (The backward pass, which takes dense tensors only.)
 int make_qkv_tensor_map(CUtensorMap* map, const void* base, int BH, int N, int box_rows, bool bf16) {
     const TensorMapKey key = {base, BH, N, box_rows + (bf16 ? 1000 : 0)};
     TensorMapSlot& slot = tensor_map_slot(key);
@@ -243,10 +301,10 @@ cudaError_t launch_plain(void (*kernel)(KArgs...), unsigned blocks, unsigned thr
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...);
 }
 
-template <bool kBf16, bool kSplitP, int kLists>
+template <bool kBf16, bool kSplitP, int kLists, bool kFourD>
 int launch_attention(DeviceInfo* dev, int slot, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                      const CUtensorMap& to, const CUtensorMap& tm, const sma::AttnArgs& args, cudaStream_t stream) {
-    auto kernel = sma::attn_fwd_kernel<kBf16, kSplitP, kLists>;
+    auto kernel = sma::attn_fwd_kernel<kBf16, kSplitP, kLists, kFourD>;
     constexpr size_t smem = sma::attn_smem_bytes();
     // One CTA per SM: the kernel allocates all 512 tensor-memory columns, and more than half of the
     // SM's shared memory keeps a second CTA from becoming resident next to it.
@@ -265,6 +323,21 @@ int launch_attention(DeviceInfo* dev, int slot, const CUtensorMap& tq, const CUt
     return cuda_ok(launch_overlapped(kernel, blocks, sma::kAttnThreads, smem, stream, tq, tk, tv, to, tm, args))
                ? SMA_OK
                : SMA_ERR_CUDA;
+}
+
+// fmt: 0 fp16, 1 bf16 with P = hi + lo, 2 bf16 with P rounded once
+template <int kLists>
+int launch_attention_fmt(int fmt, bool four_d, DeviceInfo* dev, int slot, const CUtensorMap& tq, const CUtensorMap& tk,
+                         const CUtensorMap& tv, const CUtensorMap& to, const CUtensorMap& tm, const sma::AttnArgs& args,
+                         cudaStream_t stream) {
+    if (fmt == 0)
+        return four_d ? launch_attention<false, false, kLists, true>(dev, slot, tq, tk, tv, to, tm, args, stream)
+                      : launch_attention<false, false, kLists, false>(dev, slot, tq, tk, tv, to, tm, args, stream);
+    if (fmt == 1)
+        return four_d ? launch_attention<true, true, kLists, true>(dev, slot, tq, tk, tv, to, tm, args, stream)
+                      : launch_attention<true, true, kLists, false>(dev, slot, tq, tk, tv, to, tm, args, stream);
+    return four_d ? launch_attention<true, false, kLists, true>(dev, slot, tq, tk, tv, to, tm, args, stream)
+                  : launch_attention<true, false, kLists, false>(dev, slot, tq, tk, tv, to, tm, args, stream);
 }
 
 }  // namespace
@@ -333,6 +406,9 @@ const char* sma_strerror(int status) {
             return "B*H*N is too large for the built-in workspace of sma_attention_fwd_static_workspace "
                    "(SMA_STATIC_WORKSPACE_BYTES); use sma_attention_fwd or sma_attention_fwd_planned";
         case SMA_ERR_BAD_VARIANT: return "unknown kernel variant";
+        case SMA_ERR_BAD_STRIDE:
+            return "strides of q/k/v/out must be positive multiples of 8 elements (or all zero for the dense layout); "
+                   "the backward pass takes dense tensors only";
         default: return "unknown status";
     }
 }
@@ -438,15 +514,22 @@ static int attention_forward(const sma_attention_params* p, uint32_t* plan, cons
         default: return SMA_ERR_BAD_VARIANT;
     }
 
+    int64_t sq[3], sk[3], sv[3], so[3];
+    if (!resolve_strides(p->q_strides, p->H, p->N, sq) || !resolve_strides(p->k_strides, p->H, p->N, sk) ||
+        !resolve_strides(p->v_strides, p->H, p->N, sv) || !resolve_strides(p->out_strides, p->H, p->N, so))
+        return SMA_ERR_BAD_STRIDE;
     DeviceInfo* dev = nullptr;
     if (int st = current_device_info(&dev)) return st;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
 
+    // three-dimensional maps (cheaper for the kernel's loader warps) when batch*head is one dimension of all four
+    const auto linear = [&](const int64_t (&st)[3]) { return st[0] == static_cast<int64_t>(p->H) * st[1]; };
+    const bool four_d = !(linear(sq) && linear(sk) && linear(sv) && linear(so));
     CUtensorMap tq, tk, tv, to, tm;
-    if (int st = make_qkv_tensor_map(&tq, p->q, static_cast<int>(BH), p->N, sma::kBlockM, bf16)) return st;
-    if (int st = make_qkv_tensor_map(&to, p->out, static_cast<int>(BH), p->N, sma::kStageRowsOut, bf16)) return st;
-    if (int st = make_qkv_tensor_map(&tk, p->k, static_cast<int>(BH), p->N, sma::kBlockN, bf16)) return st;
-    if (int st = make_qkv_tensor_map(&tv, p->v, static_cast<int>(BH), p->N, sma::kBlockN, bf16)) return st;
+    if (int st = make_strided_tensor_map(&tq, p->q, p->B, p->H, p->N, sq, sma::kBlockM, bf16, four_d)) return st;
+    if (int st = make_strided_tensor_map(&to, p->out, p->B, p->H, p->N, so, sma::kStageRowsOut, bf16, four_d)) return st;
+    if (int st = make_strided_tensor_map(&tk, p->k, p->B, p->H, p->N, sk, sma::kBlockN, bf16, four_d)) return st;
+    if (int st = make_strided_tensor_map(&tv, p->v, p->B, p->H, p->N, sv, sma::kBlockN, bf16, four_d)) return st;
     const bool mask_tma = mask_has_tensor_map(p->mask_packed, p->N);
     if (mask_tma) {
         if (int st = make_mask_tensor_map(&tm, p->mask_packed, static_cast<int>(BH), p->N)) return st;
@@ -462,6 +545,7 @@ static int attention_forward(const sma_attention_params* p, uint32_t* plan, cons
     args.plan_stride = sma::plan_stride_words(p->N);
     args.lse = p->lse;
     args.BH = static_cast<int32_t>(BH);
+    args.H = p->H;
     args.N = p->N;
     args.num_q_tiles = num_q_tiles;
     args.scale_log2e = std::fabs(p->scale) * 1.4426950408889634f;
@@ -469,25 +553,21 @@ static int attention_forward(const sma_attention_params* p, uint32_t* plan, cons
     args.save_lse = p->save_lse ? 1 : 0;
     args.mask_tma = mask_tma ? 1 : 0;
 
-    if (plan || tile_bits) {
-        if (plan) {
-            const unsigned items = static_cast<unsigned>(BH * num_q_tiles);
-            if (!cuda_ok(launch_plain(sma::build_tile_lists_kernel, items, sma::kPlanRows, 0, stream, p->mask_packed, plan,
-                                      static_cast<int>(BH), p->N, num_q_tiles, args.plan_stride, work_counter)))
-                return SMA_ERR_CUDA;
-        }
-        if (plan) {
-            if (!bf16) return launch_attention<false, false, sma::kListsFromPlan>(dev, 4, tq, tk, tv, to, tm, args, stream);
-            if (split_p) return launch_attention<true, true, sma::kListsFromPlan>(dev, 5, tq, tk, tv, to, tm, args, stream);
-            return launch_attention<true, false, sma::kListsFromPlan>(dev, 6, tq, tk, tv, to, tm, args, stream);
-        }
-        if (!bf16) return launch_attention<false, false, sma::kListsFromBits>(dev, 8, tq, tk, tv, to, tm, args, stream);
-        if (split_p) return launch_attention<true, true, sma::kListsFromBits>(dev, 9, tq, tk, tv, to, tm, args, stream);
-        return launch_attention<true, false, sma::kListsFromBits>(dev, 10, tq, tk, tv, to, tm, args, stream);
+    if (plan) {
+        const unsigned items = static_cast<unsigned>(BH * num_q_tiles);
+        if (!cuda_ok(launch_plain(sma::build_tile_lists_kernel, items, sma::kPlanRows, 0, stream, p->mask_packed, plan,
+                                  static_cast<int>(BH), p->N, num_q_tiles, args.plan_stride, work_counter)))
+            return SMA_ERR_CUDA;
     }
-    if (!bf16) return launch_attention<false, false, sma::kListsFromStrips>(dev, 0, tq, tk, tv, to, tm, args, stream);
-    if (split_p) return launch_attention<true, true, sma::kListsFromStrips>(dev, 1, tq, tk, tv, to, tm, args, stream);
-    return launch_attention<true, false, sma::kListsFromStrips>(dev, 2, tq, tk, tv, to, tm, args, stream);
+    // one instantiation per (element type, P format, source of the tile lists, rank of the tensor maps)
+    const int lists = plan ? sma::kListsFromPlan : tile_bits ? sma::kListsFromBits : sma::kListsFromStrips;
+    const int fmt = !bf16 ? 0 : split_p ? 1 : 2;
+    const int slot = ((lists * 3) + fmt) * 2 + (four_d ? 1 : 0);
+    if (lists == sma::kListsFromPlan)
+        return launch_attention_fmt<sma::kListsFromPlan>(fmt, four_d, dev, slot, tq, tk, tv, to, tm, args, stream);
+    if (lists == sma::kListsFromBits)
+        return launch_attention_fmt<sma::kListsFromBits>(fmt, four_d, dev, slot, tq, tk, tv, to, tm, args, stream);
+    return launch_attention_fmt<sma::kListsFromStrips>(fmt, four_d, dev, slot, tq, tk, tv, to, tm, args, stream);
 }
 
 static size_t plan_lists_bytes(long long items, int32_t N) {
@@ -564,6 +644,11 @@ int sma_attention_bwd(const sma_attention_params* p, const void* dout, void* dq,
     if (p->dtype != SMA_DTYPE_F16 && p->dtype != SMA_DTYPE_BF16) return SMA_ERR_BAD_DTYPE;
     if (p->N > SMA_MAX_SEQ_LEN) return SMA_ERR_SEQ_TOO_LONG;
     if (!std::isfinite(p->scale) || p->scale == 0.f) return SMA_ERR_BAD_SCALE;
+    for (const int64_t* st : {p->q_strides, p->k_strides, p->v_strides, p->out_strides}) {
+        const bool zero = st[0] == 0 && st[1] == 0 && st[2] == 0;
+        const bool dense = st[0] == static_cast<int64_t>(p->H) * p->N * 64 && st[1] == static_cast<int64_t>(p->N) * 64 && st[2] == 64;
+        if (!zero && !dense) return SMA_ERR_BAD_STRIDE;
+    }
     const size_t need = sma_attention_bwd_workspace_bytes(p->B, p->H, p->N);
     if (need == 0) return SMA_ERR_BAD_SHAPE;
     if (workspace_bytes < need) return SMA_ERR_WORKSPACE_TOO_SMALL;

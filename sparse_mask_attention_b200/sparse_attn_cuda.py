@@ -13,6 +13,8 @@ Differences from the reference binding, all on the safe side:
 """
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
 from . import _capi
@@ -81,9 +83,19 @@ def pack_mask(mask: torch.Tensor) -> torch.Tensor:
     return packed
 
 
-def _params_for(q, k, v, out, lse, scale, is_training):
-    """Checks q/k/v/out/lse against one another (one pass) and fills the argument block; returns it with q, k, v
-    made contiguous (the caller keeps them alive until the launch has been issued)."""
+def _strided_ok(t: torch.Tensor) -> bool:
+    """Whether the library can address ``t`` ([B, H, N, 64]) in place: rows contiguous, every other stride a positive
+    multiple of 8 elements (16 bytes), base 16-byte aligned."""
+    if t.is_contiguous():
+        return True
+    s = t.stride()
+    return s[3] == 1 and s[0] > 0 and s[1] > 0 and s[2] > 0 and (s[0] | s[1] | s[2]) % 8 == 0 and t.data_ptr() % 16 == 0
+
+
+def _params_for(q, k, v, out, lse, scale, is_training, dense: bool = False):
+    """Checks q/k/v/out/lse against one another (one pass) and fills the argument block; returns it with the q, k, v
+    it points to (the caller keeps them alive until the launch has been issued).  ``dense``: copy anything that is
+    not in the dense layout (the backward pass takes no strides)."""
     _require(q.is_cuda, "q must be CUDA tensor")
     _require(q.dim() == 4, "q must be 4D")
     dtype = _DTYPES.get(q.dtype)
@@ -96,23 +108,33 @@ def _params_for(q, k, v, out, lse, scale, is_training):
             _require(t.shape == q.shape, "%s must have the shape of q" % name)
             _require(t.dtype == q.dtype, "%s must have the dtype of q" % name)
             _require(t.device == q.device, "%s must be on the device of q" % name)
-    _require(out.is_contiguous(), "out must be contiguous")
     save_lse = bool(is_training)
     if save_lse:
         _require(lse is not None, "lse is required when is_training is true")
         _require(lse.device == q.device and lse.dtype == torch.float32, "lse must be float32 on the device of q")
         _require(tuple(lse.shape) == (B, H, N) and lse.is_contiguous(), "lse must be contiguous [B, H, N]")
-    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    # The library reads q, k, v and writes out through their own strides as long as rows are contiguous and every
+    # other stride is a multiple of 16 bytes (a view into a packed projection, a transposed [B, N, H, 64] tensor ...);
+    # only other layouts are copied to the dense one, which is what the reference's binding always does
+    # (csrc/binding.cpp:28-33).
+    if dense:
+        q, k, v, out = q.contiguous(), k.contiguous(), v.contiguous(), out.contiguous()  # out is an input there
+    else:
+        q, k, v = (t if _strided_ok(t) else t.contiguous() for t in (q, k, v))
+        _require(_strided_ok(out), "out must have contiguous rows and strides that are multiples of 8 elements")
     params = _capi.AttentionParams()
     params.q, params.k, params.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
     params.out = out.data_ptr()
+    for name, t in (("q_strides", q), ("k_strides", k), ("v_strides", v), ("out_strides", out)):
+        if not t.is_contiguous():
+            setattr(params, name, (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2)))
     params.lse = lse.data_ptr() if save_lse else None
     params.B, params.H, params.N, params.D = B, H, N, D
     params.scale = float(scale)
     params.dtype = dtype
     params.save_lse = int(save_lse)
     params.variant = int(variant)
-    return params, (q, k, v)
+    return params, (q, k, v, out)
 
 
 def forward(q, k, v, mask_packed, out, lse, scale, is_training) -> None:
@@ -137,7 +159,7 @@ def backward(dout, q, k, v, out, lse, mask_packed, dq, dk, dv, scale) -> None:
     """Gradients of the fused attention: writes ``dq``, ``dk``, ``dv`` in place.  The argument list is the one the
     reference's autograd function passes to ``sparse_attn_cuda.backward`` (python/sparse_attention.py:90-94), a
     function its extension never got; the gradient is that of its PyTorch branch (python/sparse_attention.py:96-111)."""
-    params, keep = _params_for(q, k, v, out, lse, scale, True)
+    params, keep = _params_for(q, k, v, out, lse, scale, True, dense=True)
     B, H, N = params.B, params.H, params.N
     for name, t in (("dout", dout), ("dq", dq), ("dk", dk), ("dv", dv)):
         _require(t.shape == q.shape and t.dtype == q.dtype and t.device == q.device, "%s must match q" % name)

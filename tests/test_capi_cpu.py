@@ -41,10 +41,11 @@ def test_status_codes_and_messages_match_the_header():
 
 
 def test_params_struct_layout_matches_the_header():
-    # 6 pointers, 4 int32, float, 3 int32 on an LP64 machine: 80 bytes
-    assert ctypes.sizeof(_capi.AttentionParams) == 6 * 8 + 8 * 4
+    # 6 pointers, 4 int32, float, 3 int32, then 4 x 3 int64 strides on an LP64 machine: 176 bytes
+    assert ctypes.sizeof(_capi.AttentionParams) == 6 * 8 + 8 * 4 + 12 * 8
     assert _capi.AttentionParams.B.offset == 48 and _capi.AttentionParams.scale.offset == 64
     assert _capi.AttentionParams.variant.offset == 76
+    assert _capi.AttentionParams.q_strides.offset == 80 and _capi.AttentionParams.out_strides.offset == 152
 
 
 def _params(**kw):
@@ -71,6 +72,9 @@ def _params(**kw):
     (dict(scale=float("nan")), _capi.SMA_ERR_BAD_SCALE),
     (dict(scale=float("inf")), _capi.SMA_ERR_BAD_SCALE),
     (dict(k=0x1008), _capi.SMA_ERR_MISALIGNED),
+    (dict(q_strides=(ctypes.c_int64 * 3)(4096, 64, 100)), _capi.SMA_ERR_BAD_STRIDE),     # not a multiple of 8 elements
+    (dict(v_strides=(ctypes.c_int64 * 3)(4096, 0, 64)), _capi.SMA_ERR_BAD_STRIDE),       # zero among non-zero strides
+    (dict(out_strides=(ctypes.c_int64 * 3)(-4096, 64, 64)), _capi.SMA_ERR_BAD_STRIDE),
     (dict(mask_packed=0x1002), _capi.SMA_ERR_MISALIGNED),
     (dict(variant=99), _capi.SMA_ERR_BAD_VARIANT),
     (dict(variant=_capi.SMA_VARIANT_BF16_SINGLE_P), _capi.SMA_ERR_BAD_VARIANT),  # fp16 has no such variant
