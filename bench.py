@@ -188,27 +188,45 @@ def run_reference_arm(args, cfg, rank: int):
 
 
 def bind_to_gpu_numa_node(dev_index: int):
-    """Pins this process to the CPU cores of the NUMA node its GPU hangs off, so that the pinned host buffers
-    allocated afterwards (first touch) and the copy threads sit next to the GPU's PCIe root.  Best effort:
-    returns the node number, or None when the topology cannot be read (the affinity is then left alone)."""
+    """Pins this process to the CPU cores next to its GPU, so that the pinned host buffers allocated afterwards
+    (first touch) and the copy threads sit on the GPU's side of the host.  The cores come from sysfs (the NUMA node of
+    the GPU's PCI device) or, where a container hides that, from the driver (NVML's ideal CPU affinity of the device).
+    Best effort: returns what it bound to ("node 1", "nvml 48 cpus"), or None when neither source answers (the
+    affinity is then left alone)."""
+    have = set(os.sched_getaffinity(0))
     try:
-        bus = torch.cuda.get_device_properties(dev_index).pci_bus_id
-        dom = torch.cuda.get_device_properties(dev_index).pci_domain_id
-        devid = torch.cuda.get_device_properties(dev_index).pci_device_id
-        path = "/sys/bus/pci/devices/%04x:%02x:%02x.0/numa_node" % (dom, bus, devid)
+        props = torch.cuda.get_device_properties(dev_index)
+        path = "/sys/bus/pci/devices/%04x:%02x:%02x.0/numa_node" % (props.pci_domain_id, props.pci_bus_id, props.pci_device_id)
         node = int(open(path).read().strip())
-        if node < 0:
-            return None
-        cpus = set()
-        for part in open("/sys/devices/system/node/node%d/cpulist" % node).read().strip().split(","):
-            lo, _, hi = part.partition("-")
-            cpus.update(range(int(lo), int(hi or lo) + 1))
-        allowed = cpus & set(os.sched_getaffinity(0))
-        if allowed:
-            os.sched_setaffinity(0, allowed)
-        return node
+        if node >= 0:
+            cpus = set()
+            for part in open("/sys/devices/system/node/node%d/cpulist" % node).read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+            if cpus & have:
+                os.sched_setaffinity(0, cpus & have)
+                return "node %d" % node
     except Exception:
-        return None
+        pass
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        try:
+            props = torch.cuda.get_device_properties(dev_index)
+            handle = pynvml.nvmlDeviceGetHandleByPciBusId(
+                "%08x:%02x:%02x.0" % (props.pci_domain_id, props.pci_bus_id, props.pci_device_id))
+            words = pynvml.nvmlDeviceGetCpuAffinity(handle, (os.cpu_count() + 63) // 64)
+            cpus = {64 * w + b for w, word in enumerate(words) for b in range(64) if (word >> b) & 1}
+        finally:
+            pynvml.nvmlShutdown()
+        # an affinity that names every core says nothing about the topology
+        if cpus & have and len(cpus) < os.cpu_count():
+            os.sched_setaffinity(0, cpus & have)
+            return "nvml %d cpus" % len(cpus & have)
+    except Exception:
+        pass
+    return None
 
 
 def main():
@@ -254,6 +272,7 @@ def main():
 
         dist = dist_mod
         dist.init_process_group("nccl", device_id=dev)
+    host_affinity = set(os.sched_getaffinity(0))  # the CPU baseline leg gets the whole host back
     numa_node = bind_to_gpu_numa_node(local_rank)
 
     peaks, peaks_kind = load_peaks()
@@ -606,6 +625,12 @@ def main():
     if comparators is not None:
         line["comparators"] = comparators
     if not args.no_cpu_baseline and world == 1:
+        # every thread of the process (torch's worker pool was started while the process was bound to the GPU's cores)
+        for tid in os.listdir("/proc/self/task"):
+            try:
+                os.sched_setaffinity(int(tid), host_affinity)
+            except OSError:
+                pass
         sample_B = B if N <= 512 else max(1, B // 4)
         tf, dt, cores, passes = cpu_reference_tflops(workloads, cfg, 3, 1, sample_B, min_seconds=10.0)
         line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port",
