@@ -460,6 +460,34 @@ def main():
         for p in (0.05, 0.5, 1.0):
             measure_config("keep_prob_%g" % p, dataclasses.replace(base5, name="cfg5_shard_keep%g" % p, keep_prob=p), 2, 20)
 
+        # ---- the same step as a CUDA graph: what the host pays per step when the caller captures the call ----
+        def measure_graph():
+            gq, gk, gv, gm = sets[0]
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(stream)
+            with torch.cuda.stream(side):
+                for _ in range(3):
+                    sparse_attention_func(gq, gk, gv, gm)
+            stream.wait_stream(side)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                sparse_attention_func(gq, gk, gv, gm)
+            ms = alone_ms(lambda i: graph.replay(), 50)
+            t0 = time.perf_counter()
+            for _ in range(200):
+                graph.replay()
+            host_us = (time.perf_counter() - t0) / 200 * 1e6
+            torch.cuda.synchronize(dev)
+            _capi.device_status()
+            return {"ms_per_step": ms, "host_issue_us_per_step": host_us,
+                    "what": "sparse_attention_func captured once into a torch.cuda.CUDAGraph and replayed on one input set "
+                            "(inputs stay in L2 between replays, unlike the timed regions above)"}
+
+        try:
+            other_configs["cuda_graph_replay"] = measure_graph()
+        except Exception as e:
+            other_configs["cuda_graph_replay"] = {"error": repr(e)[:200]}
+
         # ---- the backward pass at the bench workload (not part of the headline metric, which is forward only) ----
         def measure_backward():
             q0, k0, v0, m0 = sets[0]
