@@ -70,8 +70,10 @@ struct BwdSmem {
     uint64_t bar_qdo_free;  // tensor core: the products that read the step's Q and dO tiles (dV, dK) are complete
     uint32_t tmem_base;
     uint32_t abort_flag;
-    uint32_t next_unit;     // the unit this CTA takes after the one in work
-    uint32_t qblock_any[kBwdMaxQBlocks / 32];  // bit i: query block i keeps something in the keys of the unit in work
+    // Double-buffered by the parity of the CTA's unit count: while a unit is in work the control warp names the one
+    // after it and marks that unit's query blocks.
+    uint32_t unit_id[2];                          // the unit (>= the number of units: none is left)
+    uint32_t qblock_any[2][kBwdMaxQBlocks / 32];  // bit i: query block i keeps something in the keys of the unit
 };
 
 constexpr size_t bwd_smem_bytes() { return sizeof(BwdSmem) + 1024; }
@@ -181,9 +183,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     auto wait = [&](uint32_t bar, uint32_t parity) {
         if (ok) ok = __all_sync(0xFFFFFFFFu, mbar_wait_a(bar, parity, abort_flag));
     };
-    // next query block >= i that keeps something, or nblk
-    auto next_block = [&](int i) {
-        while (i < nblk && !((sm.qblock_any[i >> 5] >> (i & 31)) & 1u)) ++i;
+    // next query block >= i that keeps something (by the flags in `slot`), or nblk
+    auto next_block = [&](uint32_t slot, int i) {
+        while (i < nblk && !((sm.qblock_any[slot][i >> 5] >> (i & 31)) & 1u)) ++i;
         return i;
     };
 
@@ -236,38 +238,111 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             }
             __syncwarp();
         };
-        for (long long u = blockIdx.x; u < units;) {
+        // Which query blocks keep anything in the 128 keys of a unit: the control warp reads the unit's column strip of
+        // the mask (plain loads: this kernel is launched the ordinary way, everything written before it is visible),
+        // four query blocks at a time, one lane per four rows of a block.  It does so for the unit AFTER the one in
+        // work, between its other duties, so that at a unit's end the next unit's tiles can be requested at once.
+        const bool scan_vec = (nw & 3) == 0 && (reinterpret_cast<uintptr_t>(args.mask_packed) & 15u) == 0;
+        const uint32_t* scan_strip = nullptr;
+        int scan_words = 0, scan_blk = nblk;
+        auto scan_begin = [&](long long us, uint32_t slot) {
+            if (lane < kBwdMaxQBlocks / 32) sm.qblock_any[slot][lane] = 0u;
+            __syncwarp();
+            scan_blk = nblk;
+            if (us < units) {
+                const int jj = static_cast<int>(us / args.BH), bb = static_cast<int>(us % args.BH);
+                scan_strip = args.mask_packed + static_cast<size_t>(bb) * N * nw + 4 * jj;
+                scan_words = nw - 4 * jj < 4 ? nw - 4 * jj : 4;
+                scan_blk = 0;
+            }
+        };
+        // The loads of four query blocks are requested in one call and looked at in the next (a step later): the warp
+        // never stands waiting for them with products to issue.
+        uint4 pend[16];
+        int pend_blk = -1;  // the first of the four blocks whose words are on their way, or none
+        auto scan_step = [&](uint32_t slot) {
+            if (pend_blk >= 0) {
+                uint32_t bits = 0u;
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    uint32_t any = 0u;
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) any |= pend[4 * b + r].x | pend[4 * b + r].y | pend[4 * b + r].z | pend[4 * b + r].w;
+                    if (__any_sync(0xFFFFFFFFu, any != 0u)) bits |= 1u << b;
+                }
+                if (lane == 0 && bits != 0u) sm.qblock_any[slot][pend_blk >> 5] |= bits << (pend_blk & 31);  // pend_blk % 4 == 0
+                __syncwarp();
+                pend_blk = -1;
+            }
+            if (scan_blk < nblk) {
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        uint4 x = make_uint4(0u, 0u, 0u, 0u);
+                        const int row = (scan_blk + b) * kBwdBlock + lane + 32 * r;  // (past the last block: past N as well)
+                        if (row < N) {
+                            const uint32_t* mrow = scan_strip + static_cast<size_t>(row) * nw;
+                            if (scan_vec) {
+                                x = *reinterpret_cast<const uint4*>(mrow);
+                            } else {
+                                x.x = mrow[0];
+                                if (scan_words > 1) x.y = mrow[1];
+                                if (scan_words > 2) x.z = mrow[2];
+                                if (scan_words > 3) x.w = mrow[3];
+                            }
+                        }
+                        pend[4 * b + r] = x;
+                    }
+                }
+                pend_blk = scan_blk;
+                scan_blk += 4;
+            }
+        };
+        auto scan_pending = [&]() { return pend_blk >= 0 || scan_blk < nblk; };
+        // K_j, V_j and the first Q/dO tiles of unit u, whose flags are in `slot`; i = its first query block
+        int i = nblk;
+        long long u = blockIdx.x;  // < units: the grid has at most one CTA per unit
+        auto load_unit = [&](uint32_t slot) {
             begin_unit(u);
-            __syncthreads();  // the unit before is over for every thread; its query-block flags have been cleared
-            if (*abort_flag) break;
-            // K_j and V_j, which the unit needs whatever the scan finds, and the unit after this one
-            if (leader) {
+            i = next_block(slot, 0);
+            if (leader && ok) {
                 mbar_arrive_expect_tx_a(a_bar_kv, 2 * kBwdTileBytes);
                 tma_load_3d_a(smem_u32(sm.k), &tmap_k, a_bar_kv, 0, j * kBwdBlock, bh);
                 tma_load_3d_a(smem_u32(sm.v), &tmap_v, a_bar_kv, 0, j * kBwdBlock, bh);
-                const long long next = args.unit_counter != nullptr
-                                           ? static_cast<long long>(gridDim.x) + atomicAdd(args.unit_counter, 1u)
-                                           : u + gridDim.x;
-                sm.next_unit = static_cast<uint32_t>(next < units ? next : units);
             }
             __syncwarp();
-            __syncthreads();  // the compute warps have scanned the unit's column strip of the mask
-            const long long u_next = sm.next_unit;
+            if (i < nblk) load_q_do(g & 1u, i);
+        };
+        scan_begin(u, 0u);
+        while (scan_pending()) scan_step(0u);
+        if (lane == 0) sm.unit_id[0] = static_cast<uint32_t>(u);
+        __syncwarp();
+        load_unit(0u);
+        for (;;) {
+            // The unit before is over for every thread (its accumulators have left tensor memory, nobody reads its flags
+            // any more); the compute warps find this unit's number and flags, written during the unit before.
+            __syncthreads();
+            if (u >= units || *abort_flag) break;
+            const uint32_t slot = unit_no & 1u;
             uint32_t s = 0;  // steps of this unit
-            int i = next_block(0);
-            if (i < nblk) {
-                load_q_do(g & 1u, i);
-                wait(a_bar_qdo + 8 * (g & 1u), (g >> 1) & 1u);
-            }
+            // the unit after this one: asked for now, looked at behind the first products (the answer takes a while)
+            long long next = u + gridDim.x;
+            if (leader && args.unit_counter != nullptr) next = static_cast<long long>(gridDim.x) + atomicAdd(args.unit_counter, 1u);
+            if (i < nblk) wait(a_bar_qdo + 8 * (g & 1u), (g >> 1) & 1u);
             wait(a_bar_kv, unit_no & 1u);  // also in a unit whose keys nobody keeps: the copy lands before the buffers are reused
             if (i < nblk) issue_s_dp(g & 1u);
+            if (leader) sm.unit_id[slot ^ 1u] = static_cast<uint32_t>(next < units ? next : units);
+            __syncwarp();
+            const long long u_next = sm.unit_id[slot ^ 1u];
+            scan_begin(u_next, slot ^ 1u);
             // Step: as soon as the compute warps have turned S and dP of a block into P and dS, the tensor core gets S
             // and dP of the next block (which the compute warps then work on) and, behind them, the three products
             // that consume P and dS of this one.  P/dS, Q/dO and dQ exist twice, so the products of a block run under
             // the arithmetic of the next.
             while (i < nblk && ok) {
                 const uint32_t st = g & 1u;
-                const int i_next = next_block(i + 1);
+                const int i_next = next_block(slot, i + 1);
                 if (i_next < nblk) {
                     // the other Q/dO stage was last read by the dV and dK products of the step before (at a unit's first
                     // step: of the unit before, long complete)
@@ -299,12 +374,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                     mma_commit_a(a_bar_mma2);
                 }
                 __syncwarp();
+                if (scan_pending()) scan_step(slot ^ 1u);  // (nothing to issue until the products above have made headway)
                 ++s;
                 ++g;
                 i = i_next;
             }
+            while (scan_pending()) scan_step(slot ^ 1u);
+            // K_j, V_j and both Q/dO stages are free once the last step's products are complete: the next unit's tiles
+            // travel while the compute warps take this unit's dQ, dK and dV out of tensor memory
+            if (s >= 1) wait(a_bar_mma2, (g - 1) & 1u);
             u = u_next;
             ++unit_no;
+            i = nblk;
+            if (u < units) load_unit(slot ^ 1u);
         }
     } else {
         // ================= two threads per query row (64 keys each): P, dS, dQ, and at the end dK, dV =================
@@ -380,45 +462,20 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             }
             return r;
         };
-        const int trow = t;
-        for (long long u = blockIdx.x; u < units;) {
+        for (;;) {
+            // The unit before is over for every thread; the control warp has named this one and marked the query blocks
+            // that keep anything in its keys.
+            __syncthreads();
+            const uint32_t slot = unit_no & 1u;
+            const long long u = sm.unit_id[slot];
+            if (u >= units || *abort_flag) break;
             begin_unit(u);
-            if (threadIdx.x < kBwdMaxQBlocks / 32) sm.qblock_any[threadIdx.x] = 0u;  // (nobody reads the old flags any more)
-            __syncthreads();  // the unit before is over for every thread; the flags are clear
-            if (*abort_flag) break;
-            // Which query blocks keep anything in keys 128j..128j+127: thread t looks at row t of every block (warps 0-3
-            // the even blocks, warps 4-7 the odd ones).  Plain loads (this kernel is launched the ordinary way: everything
-            // written before it is visible), and all loads of a batch of four blocks before the first ballot: the
-            // shared-memory atomic below keeps the compiler from moving later loads above it, and one block at a time
-            // the scan paid a full memory latency per block.
-            for (int i0 = warp >> 2; i0 < nblk; i0 += 8) {
-                uint32_t any[4];
-#pragma unroll
-                for (int b = 0; b < 4; ++b) {
-                    const int ib = i0 + 2 * b, row = ib * kBwdBlock + trow;
-                    any[b] = 0u;
-                    if (ib < nblk && row < N) {
-                        const uint32_t* mrow = mask_bh + static_cast<size_t>(row) * nw + 4 * j;
-#pragma unroll
-                        for (int w = 0; w < 4; ++w)
-                            if (4 * j + w < nw) any[b] |= mrow[w];
-                    }
-                }
-#pragma unroll
-                for (int b = 0; b < 4; ++b) {
-                    const int ib = i0 + 2 * b;
-                    const uint32_t some = __ballot_sync(0xFFFFFFFFu, any[b] != 0u);
-                    if (lane == 0 && some != 0u) atomicOr(&sm.qblock_any[ib >> 5], 1u << (ib & 31));
-                }
-            }
-            __syncthreads();  // the flags are complete (and the control warp has named the next unit)
-            const long long u_next = sm.next_unit;
             uint32_t steps = 0;  // steps of this unit
-        int i = next_block(0);
+        int i = next_block(slot, 0);
         RowIn in_next = load_row(i);
         while (i < nblk && ok) {
             const RowIn in = in_next;
-            const int i_next = next_block(i + 1);
+            const int i_next = next_block(slot, i + 1);
             in_next = load_row(i_next);
             uint32_t mw[2] = {in.mw0, in.mw1};
             float neg_lse_l2 = 0.f;
@@ -506,10 +563,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 for (int c = 0; c < kBwdDim / 8; ++c) dst[c] = make_uint4(outw[4 * c], outw[4 * c + 1], outw[4 * c + 2], outw[4 * c + 3]);
             }
         }
-            // (the next unit's first products overwrite dK and dV in tensor memory: they are issued behind two CTA-wide
-            // barriers that this thread reaches after the loads above have completed)
+            // (the next unit's products that overwrite dK and dV in tensor memory are issued behind the CTA-wide barrier
+            // above, which this thread reaches after the loads have completed)
             tc_fence_before_sync();
-            u = u_next;
             ++unit_no;
         }
         if (reducer) tma_store_wait_all();  // the reductions are complete before the CTA (and its shared memory) goes
