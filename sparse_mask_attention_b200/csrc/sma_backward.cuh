@@ -45,7 +45,7 @@ namespace sma {
 constexpr int kBwdBlock = 128;              // query rows per step, and keys per CTA
 constexpr int kBwdDim = 64;                 // head dimension
 constexpr int kBwdComputeWarps = 8;         // two threads per query row: 64 keys each
-constexpr int kBwdThreads = 32 * (kBwdComputeWarps + 1);  // + the warp that loads and issues
+constexpr int kBwdThreads = 32 * (kBwdComputeWarps + 2);  // + the warp that issues the products + the warp that loads
 constexpr uint32_t kBwdTileBytes = kBwdBlock * kBwdDim * 2;  // [128 rows][64] 16-bit
 constexpr uint32_t kBwdPanelBytes = kBwdBlock * 128;         // [128 query rows][64 keys] 16-bit
 constexpr uint32_t kBwdTmemCols = 512;
@@ -60,14 +60,17 @@ struct BwdSmem {
     alignas(1024) uint8_t p[2][2][kBwdPanelBytes];   // [step % 2][panel of 64 keys]
     alignas(1024) uint8_t ds[2][2][kBwdPanelBytes];
     uint64_t bar_kv;        // TMA: K_j and V_j landed
-    uint64_t bar_qdo[2];    // TMA: Q_i and dO_i landed in stage s
+    uint64_t bar_q[2];      // TMA: Q_i landed in stage s
+    uint64_t bar_do[2];     // TMA: dO_i landed in stage s
     uint64_t bar_sdp;       // tensor core: S and dP of the step are complete
     uint64_t bar_sfree;     // all compute threads: S and dP of the step have been read out of tensor memory
     uint64_t bar_pds;       // all compute threads: P and dS of the step are in shared memory, its S and dP and the
-                            // dQ of the step before have been read out of tensor memory
+                            // dQ of the step before last have been read out of tensor memory
     uint64_t bar_mma2;      // tensor core: dV, dK accumulated and dQ complete for the step
     uint64_t bar_half[2];   // the 128 compute threads of a half meet here (a bounded wait, unlike bar.sync)
-    uint64_t bar_qdo_free;  // tensor core: the products that read the step's Q and dO tiles (dV, dK) are complete
+    uint64_t bar_q_free;    // tensor core: the last product that reads the step's Q tile (dK) is complete
+    uint64_t bar_do_free;   // tensor core: the last product that reads the step's dO tile (dV) is complete
+    uint64_t bar_done;      // tensor core: every product of the unit is complete (one phase per unit)
     uint32_t tmem_base;
     uint32_t abort_flag;
     // Double-buffered by the parity of the CTA's unit count: while a unit is in work the control warp names the one
@@ -155,13 +158,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 
     if (threadIdx.x == 0) {
         mbar_init(&sm.bar_kv, 1);
-        mbar_init(&sm.bar_qdo[0], 1);
-        mbar_init(&sm.bar_qdo[1], 1);
+        mbar_init(&sm.bar_q[0], 1);
+        mbar_init(&sm.bar_q[1], 1);
+        mbar_init(&sm.bar_do[0], 1);
+        mbar_init(&sm.bar_do[1], 1);
         mbar_init(&sm.bar_sdp, 1);
         mbar_init(&sm.bar_sfree, 32 * kBwdComputeWarps);
         mbar_init(&sm.bar_pds, 32 * kBwdComputeWarps);
         mbar_init(&sm.bar_mma2, 1);
-        mbar_init(&sm.bar_qdo_free, 1);
+        mbar_init(&sm.bar_q_free, 1);
+        mbar_init(&sm.bar_do_free, 1);
+        mbar_init(&sm.bar_done, 1);
         mbar_init(&sm.bar_half[0], 128);
         mbar_init(&sm.bar_half[1], 128);
         sm.abort_flag = 0u;
@@ -177,8 +184,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     tc_fence_after_sync();
     const uint32_t tmem = sm.tmem_base;
 
-    const uint32_t a_bar_kv = smem_u32(&sm.bar_kv), a_bar_qdo = smem_u32(&sm.bar_qdo[0]), a_bar_sdp = smem_u32(&sm.bar_sdp),
-                   a_bar_pds = smem_u32(&sm.bar_pds), a_bar_mma2 = smem_u32(&sm.bar_mma2), a_bar_sfree = smem_u32(&sm.bar_sfree);
+    const uint32_t a_bar_kv = smem_u32(&sm.bar_kv), a_bar_q = smem_u32(&sm.bar_q[0]), a_bar_do = smem_u32(&sm.bar_do[0]),
+                   a_bar_sdp = smem_u32(&sm.bar_sdp), a_bar_pds = smem_u32(&sm.bar_pds), a_bar_mma2 = smem_u32(&sm.bar_mma2),
+                   a_bar_sfree = smem_u32(&sm.bar_sfree), a_bar_q_free = smem_u32(&sm.bar_q_free),
+                   a_bar_do_free = smem_u32(&sm.bar_do_free), a_bar_done = smem_u32(&sm.bar_done);
     bool ok = true;  // false once a bounded wait has run out; the same in all lanes of a warp
     auto wait = [&](uint32_t bar, uint32_t parity) {
         if (ok) ok = __all_sync(0xFFFFFFFFu, mbar_wait_a(bar, parity, abort_flag));
@@ -195,7 +204,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         mask_bh = args.mask_packed + static_cast<size_t>(bh) * N * nw;
     };
     if (warp == kBwdComputeWarps) {
-        // ===================================== loads and tensor-core issue =====================================
+        // ========================================= tensor-core issue =========================================
         // all lanes run the control flow (operands stay in uniform registers); one elected lane issues
         const bool leader = elect_one();
         constexpr uint32_t kHi = kSmemDescSw128Hi;
@@ -208,6 +217,89 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         const uint32_t p_t_lo0 = ((smem_u32(sm.p[0][0]) & 0x3FFFFu) >> 4) | kPanelLbo;
         const uint32_t ds_t_lo0 = ((smem_u32(sm.ds[0][0]) & 0x3FFFFu) >> 4) | kPanelLbo;
         const uint32_t ds_k_lo0 = smem_desc_sw128_lo(smem_u32(sm.ds[0][0]));
+        // S = Q K^T and dP = dO V^T of the query block whose tiles arrive in stage `st`, each as soon as its tile is there
+        // (contraction over the head dimension: 16 elements = 32 bytes inside the swizzled 128-byte row).  `step` is the
+        // step the block belongs to; before S and dP are overwritten, those of the step before have left tensor memory.
+        auto issue_s_dp = [&](uint32_t step, bool first) {
+            const uint32_t st = step & 1u, ph = (step >> 1) & 1u;
+            const uint32_t q_lo = smem_desc_sw128_lo(smem_u32(sm.q[st])), do_lo = smem_desc_sw128_lo(smem_u32(sm.dout[st]));
+            wait(a_bar_q + 8 * st, ph);
+            if (!first) wait(a_bar_sfree, (step - 1) & 1u);
+            tc_fence_after_sync();
+            if (leader && ok) {
+#pragma unroll
+                for (int kk = 0; kk < kBwdDim / 16; ++kk) mma_ss_lh(tmem + kBwdColS, q_lo + 2 * kk, k_lo + 2 * kk, kHi, idesc_s, kk ? 1u : 0u);
+            }
+            __syncwarp();
+            wait(a_bar_do + 8 * st, ph);
+            if (leader && ok) {
+#pragma unroll
+                for (int kk = 0; kk < kBwdDim / 16; ++kk) mma_ss_lh(tmem + kBwdColDP, do_lo + 2 * kk, v_lo + 2 * kk, kHi, idesc_s, kk ? 1u : 0u);
+                mma_commit_a(a_bar_sdp);
+            }
+            __syncwarp();
+        };
+        for (;;) {
+            // The unit before is over for every thread (its accumulators have left tensor memory); the loading warp has
+            // named this unit and marked its query blocks during the unit before.
+            __syncthreads();
+            const uint32_t slot = unit_no & 1u;
+            if (sm.unit_id[slot] >= units || *abort_flag) break;
+            uint32_t s = 0;  // steps of this unit
+            int i = next_block(slot, 0);
+            if (i < nblk) {
+                wait(a_bar_kv, unit_no & 1u);
+                issue_s_dp(g, true);
+            }
+            // Step: as soon as the compute warps have turned S and dP of a block into P and dS, the tensor core gets S
+            // and dP of the next block (which the compute warps then work on) and, behind them, the three products
+            // that consume P and dS of this one.  P/dS, Q/dO and dQ exist twice, so the products of a block run under
+            // the arithmetic of the next.
+            while (i < nblk && ok) {
+                const uint32_t st = g & 1u;
+                const int i_next = next_block(slot, i + 1);
+                // S and dP of the next block go to the tensor core as soon as this block's have left tensor memory,
+                // while the compute warps are still busy with the arithmetic on them
+                if (i_next < nblk) issue_s_dp(g + 1, false);
+                wait(a_bar_pds, g & 1u);
+                tc_fence_after_sync();
+                const uint32_t q_lo = smem_desc_sw128_lo(smem_u32(sm.q[st])), do_lo = smem_desc_sw128_lo(smem_u32(sm.dout[st]));
+                const uint32_t p_t_lo = p_t_lo0 + st * kStageUnits, ds_t_lo = ds_t_lo0 + st * kStageUnits, ds_k_lo = ds_k_lo0 + st * kStageUnits;
+                if (leader && ok) {
+                    const uint32_t acc0 = s ? 1u : 0u;
+                    // contraction over the 128 query rows: 16 rows of 128 bytes = 2048 bytes per step, in both operands.
+                    // dK first: it is the last reader of the Q tile, which the next S needs before anything else.
+#pragma unroll
+                    for (int kk = 0; kk < kBwdBlock / 16; ++kk) mma_ss_lh(tmem + kBwdColDK, ds_t_lo + 128 * kk, q_lo + 128 * kk, kHi, idesc_t, kk ? 1u : acc0);
+                    mma_commit_a(a_bar_q_free);
+#pragma unroll
+                    for (int kk = 0; kk < kBwdBlock / 16; ++kk) mma_ss_lh(tmem + kBwdColDV, p_t_lo + 128 * kk, do_lo + 128 * kk, kHi, idesc_t, kk ? 1u : acc0);
+                    mma_commit_a(a_bar_do_free);
+                    // contraction over the 128 keys: dS is K-major, 64 keys per panel; K_j rows are keys
+#pragma unroll
+                    for (int kk = 0; kk < kBwdBlock / 16; ++kk)
+                        mma_ss_lh(tmem + kBwdColDQ + 64 * st, ds_k_lo + (kk >> 2) * (kBwdPanelBytes >> 4) + 2 * (kk & 3), k_lo + 128 * kk, kHi,
+                                  idesc_q, kk ? 1u : 0u);
+                    mma_commit_a(a_bar_mma2);
+                }
+                __syncwarp();
+                ++s;
+                ++g;
+                i = i_next;
+            }
+            // The loading warp, which runs ahead of this one, learns here that K_j, V_j and the Q/dO stages are free.
+            // (It waits for every phase of this barrier in turn; a barrier that it skipped phases of would answer for
+            // the wrong one.)
+            if (leader && ok) {
+                if (s >= 1) mma_commit_a(a_bar_done);
+                else mbar_arrive_a(a_bar_done);
+            }
+            __syncwarp();
+            ++unit_no;
+        }
+    } else if (warp == kBwdComputeWarps + 1) {
+        // ================================ loads, and the choice of the next unit ================================
+        const bool leader = elect_one();
         if (leader) {
             tma_prefetch_desc(&tmap_q);
             tma_prefetch_desc(&tmap_k);
@@ -215,33 +307,24 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             tma_prefetch_desc(&tmap_do);
         }
         __syncwarp();
-        auto load_q_do = [&](uint32_t stage, int i) {
+        auto load_q = [&](uint32_t stage, int i) {
             if (leader && ok) {
-                const uint32_t bar = a_bar_qdo + 8 * stage;
-                mbar_arrive_expect_tx_a(bar, 2 * kBwdTileBytes);
-                tma_load_3d_a(smem_u32(sm.q[stage]), &tmap_q, bar, 0, i * kBwdBlock, bh);
-                tma_load_3d_a(smem_u32(sm.dout[stage]), &tmap_do, bar, 0, i * kBwdBlock, bh);
+                mbar_arrive_expect_tx_a(a_bar_q + 8 * stage, kBwdTileBytes);
+                tma_load_3d_a(smem_u32(sm.q[stage]), &tmap_q, a_bar_q + 8 * stage, 0, i * kBwdBlock, bh);
             }
             __syncwarp();
         };
-        // S = Q K^T and dP = dO V^T of the query block in stage `st` (contraction over the head dimension: 16 elements =
-        // 32 bytes inside the swizzled 128-byte row)
-        auto issue_s_dp = [&](uint32_t st) {
-            tc_fence_after_sync();
-            const uint32_t q_lo = smem_desc_sw128_lo(smem_u32(sm.q[st])), do_lo = smem_desc_sw128_lo(smem_u32(sm.dout[st]));
+        auto load_do = [&](uint32_t stage, int i) {
             if (leader && ok) {
-#pragma unroll
-                for (int kk = 0; kk < kBwdDim / 16; ++kk) mma_ss_lh(tmem + kBwdColS, q_lo + 2 * kk, k_lo + 2 * kk, kHi, idesc_s, kk ? 1u : 0u);
-#pragma unroll
-                for (int kk = 0; kk < kBwdDim / 16; ++kk) mma_ss_lh(tmem + kBwdColDP, do_lo + 2 * kk, v_lo + 2 * kk, kHi, idesc_s, kk ? 1u : 0u);
-                mma_commit_a(a_bar_sdp);
+                mbar_arrive_expect_tx_a(a_bar_do + 8 * stage, kBwdTileBytes);
+                tma_load_3d_a(smem_u32(sm.dout[stage]), &tmap_do, a_bar_do + 8 * stage, 0, i * kBwdBlock, bh);
             }
             __syncwarp();
         };
-        // Which query blocks keep anything in the 128 keys of a unit: the control warp reads the unit's column strip of
+        // Which query blocks keep anything in the 128 keys of a unit: this warp reads the unit's column strip of
         // the mask (plain loads: this kernel is launched the ordinary way, everything written before it is visible),
         // four query blocks at a time, one lane per four rows of a block.  It does so for the unit AFTER the one in
-        // work, between its other duties, so that at a unit's end the next unit's tiles can be requested at once.
+        // work, between its loads, so that at a unit's end the next unit's tiles can be requested at once.
         const bool scan_vec = (nw & 3) == 0 && (reinterpret_cast<uintptr_t>(args.mask_packed) & 15u) == 0;
         const uint32_t* scan_strip = nullptr;
         int scan_words = 0, scan_blk = nblk;
@@ -257,7 +340,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             }
         };
         // The loads of four query blocks are requested in one call and looked at in the next (a step later): the warp
-        // never stands waiting for them with products to issue.
+        // does not stand waiting for them with tiles to request.
         uint4 pend[16];
         int pend_blk = -1;  // the first of the four blocks whose words are on their way, or none
         auto scan_step = [&](uint32_t slot) {
@@ -312,7 +395,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 tma_load_3d_a(smem_u32(sm.v), &tmap_v, a_bar_kv, 0, j * kBwdBlock, bh);
             }
             __syncwarp();
-            if (i < nblk) load_q_do(g & 1u, i);
+            if (i < nblk) {
+                load_q(g & 1u, i);
+                load_do(g & 1u, i);
+            }
         };
         scan_begin(u, 0u);
         while (scan_pending()) scan_step(0u);
@@ -320,69 +406,48 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         __syncwarp();
         load_unit(0u);
         for (;;) {
-            // The unit before is over for every thread (its accumulators have left tensor memory, nobody reads its flags
-            // any more); the compute warps find this unit's number and flags, written during the unit before.
+            // The unit before is over for every thread (nobody reads its flags any more); the other warps find this
+            // unit's number and flags, written during the unit before.
             __syncthreads();
             if (u >= units || *abort_flag) break;
             const uint32_t slot = unit_no & 1u;
             uint32_t s = 0;  // steps of this unit
-            // the unit after this one: asked for now, looked at behind the first products (the answer takes a while)
+            // the unit after this one: asked for now, looked at behind the first step's requests (the answer takes a while)
             long long next = u + gridDim.x;
             if (leader && args.unit_counter != nullptr) next = static_cast<long long>(gridDim.x) + atomicAdd(args.unit_counter, 1u);
-            if (i < nblk) wait(a_bar_qdo + 8 * (g & 1u), (g >> 1) & 1u);
-            wait(a_bar_kv, unit_no & 1u);  // also in a unit whose keys nobody keeps: the copy lands before the buffers are reused
-            if (i < nblk) issue_s_dp(g & 1u);
-            if (leader) sm.unit_id[slot ^ 1u] = static_cast<uint32_t>(next < units ? next : units);
-            __syncwarp();
-            const long long u_next = sm.unit_id[slot ^ 1u];
-            scan_begin(u_next, slot ^ 1u);
-            // Step: as soon as the compute warps have turned S and dP of a block into P and dS, the tensor core gets S
-            // and dP of the next block (which the compute warps then work on) and, behind them, the three products
-            // that consume P and dS of this one.  P/dS, Q/dO and dQ exist twice, so the products of a block run under
-            // the arithmetic of the next.
+            long long u_next = units;
+            bool named = false;
+            auto name_next = [&]() {
+                if (leader) sm.unit_id[slot ^ 1u] = static_cast<uint32_t>(next < units ? next : units);
+                __syncwarp();
+                u_next = sm.unit_id[slot ^ 1u];
+                scan_begin(u_next, slot ^ 1u);
+                named = true;
+            };
+            // A stage's Q tile is free once the dK product of the step that used it is complete, its dO tile once dV is
+            // (at a unit's first step: of the unit before, long complete).
             while (i < nblk && ok) {
                 const uint32_t st = g & 1u;
                 const int i_next = next_block(slot, i + 1);
                 if (i_next < nblk) {
-                    // the other Q/dO stage was last read by the dV and dK products of the step before (at a unit's first
-                    // step: of the unit before, long complete)
-                    if (s >= 1) wait(smem_u32(&sm.bar_qdo_free), (g - 1) & 1u);
-                    load_q_do(st ^ 1u, i_next);
-                    // S and dP of the next block go to the tensor core as soon as this block's have left tensor memory,
-                    // while the compute warps are still busy with the arithmetic on them
-                    wait(a_bar_qdo + 8 * (st ^ 1u), ((g + 1) >> 1) & 1u);
-                    wait(a_bar_sfree, g & 1u);
-                    issue_s_dp(st ^ 1u);
+                    if (s >= 1) wait(a_bar_q_free, (g - 1) & 1u);
+                    load_q(st ^ 1u, i_next);
+                    if (s >= 1) wait(a_bar_do_free, (g - 1) & 1u);
+                    load_do(st ^ 1u, i_next);
                 }
-                wait(a_bar_pds, g & 1u);
-                tc_fence_after_sync();
-                const uint32_t q_lo = smem_desc_sw128_lo(smem_u32(sm.q[st])), do_lo = smem_desc_sw128_lo(smem_u32(sm.dout[st]));
-                const uint32_t p_t_lo = p_t_lo0 + st * kStageUnits, ds_t_lo = ds_t_lo0 + st * kStageUnits, ds_k_lo = ds_k_lo0 + st * kStageUnits;
-                if (leader && ok) {
-                    const uint32_t acc0 = s ? 1u : 0u;
-                    // contraction over the 128 query rows: 16 rows of 128 bytes = 2048 bytes per step, in both operands
-#pragma unroll
-                    for (int kk = 0; kk < kBwdBlock / 16; ++kk) mma_ss_lh(tmem + kBwdColDV, p_t_lo + 128 * kk, do_lo + 128 * kk, kHi, idesc_t, kk ? 1u : acc0);
-#pragma unroll
-                    for (int kk = 0; kk < kBwdBlock / 16; ++kk) mma_ss_lh(tmem + kBwdColDK, ds_t_lo + 128 * kk, q_lo + 128 * kk, kHi, idesc_t, kk ? 1u : acc0);
-                    mma_commit_a(smem_u32(&sm.bar_qdo_free));  // (the dQ product below reads neither Q nor dO)
-                    // contraction over the 128 keys: dS is K-major, 64 keys per panel; K_j rows are keys
-#pragma unroll
-                    for (int kk = 0; kk < kBwdBlock / 16; ++kk)
-                        mma_ss_lh(tmem + kBwdColDQ + 64 * st, ds_k_lo + (kk >> 2) * (kBwdPanelBytes >> 4) + 2 * (kk & 3), k_lo + 128 * kk, kHi,
-                                  idesc_q, kk ? 1u : 0u);
-                    mma_commit_a(a_bar_mma2);
-                }
-                __syncwarp();
-                if (scan_pending()) scan_step(slot ^ 1u);  // (nothing to issue until the products above have made headway)
+                if (!named) name_next();
+                if (scan_pending()) scan_step(slot ^ 1u);
                 ++s;
                 ++g;
                 i = i_next;
             }
+            if (!named) name_next();
             while (scan_pending()) scan_step(slot ^ 1u);
-            // K_j, V_j and both Q/dO stages are free once the last step's products are complete: the next unit's tiles
-            // travel while the compute warps take this unit's dQ, dK and dV out of tensor memory
-            if (s >= 1) wait(a_bar_mma2, (g - 1) & 1u);
+            // K_j, V_j and both Q/dO stages are free once the last step's products are complete (and the K/V copy has
+            // landed, also in a unit whose keys nobody keeps): the next unit's tiles travel while the compute warps take
+            // this unit's dQ, dK and dV out of tensor memory
+            wait(a_bar_done, unit_no & 1u);
+            wait(a_bar_kv, unit_no & 1u);
             u = u_next;
             ++unit_no;
             i = nblk;
@@ -522,14 +587,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 }
             }
             fence_proxy_async_smem();
-            // dQ of the step before (its products ran under this step's arithmetic) leaves tensor memory before this
-            // thread arrives: the products of this step, issued behind the arrival, write the other dQ buffer, and the
-            // ones after them this one
-            float dq[32];
-            if (steps >= 1) read_dq(g - 1, dq);
             tc_fence_before_sync();
             mbar_arrive_a(a_bar_pds);
-            if (steps >= 1 && ok) reduce_dq(g - 1, dq, prev_row0);
+            // dQ of the step before (its products ran under this step's arithmetic) leaves tensor memory behind the
+            // arrival, which nothing then holds up: the products of this step write the other dQ buffer, and the ones
+            // after them, issued behind this thread's next arrival, this one
+            if (steps >= 1) {
+                float dq[32];
+                read_dq(g - 1, dq);
+                if (ok) reduce_dq(g - 1, dq, prev_row0);
+            }
             prev_row0 = i * kBwdBlock;
             ++steps;
             ++g;
