@@ -64,9 +64,14 @@ struct BwdSmem {
     uint64_t bar_do[2];     // TMA: dO_i landed in stage s
     uint64_t bar_sdp;       // tensor core: S and dP of the step are complete
     uint64_t bar_sfree;     // all compute threads: S and dP of the step have been read out of tensor memory
-    uint64_t bar_pds;       // all compute threads: P and dS of the step are in shared memory, its S and dP and the
+    // The next two exist once per step parity.  A thread that waits for step g of one of them may already have done
+    // everything that step g + 1 needs from it (the issuing warp has S and dP of step g + 1 out before it waits for
+    // P and dS of step g; a compute thread arrives for step g before it waits for the products of step g - 1), so on
+    // a single barrier phase g + 1 could complete before the waiter has looked, and a parity wait would then take
+    // it for phase g - 1.  Step g + 2 always needs the waiter to have moved on.
+    uint64_t bar_pds[2];    // all compute threads: P and dS of the step are in shared memory, its S and dP and the
                             // dQ of the step before last have been read out of tensor memory
-    uint64_t bar_mma2;      // tensor core: dV, dK accumulated and dQ complete for the step
+    uint64_t bar_mma2[2];   // tensor core: dV, dK accumulated and dQ complete for the step
     uint64_t bar_half[2];   // the 128 compute threads of a half meet here (a bounded wait, unlike bar.sync)
     uint64_t bar_q_free;    // tensor core: the last product that reads the step's Q tile (dK) is complete
     uint64_t bar_do_free;   // tensor core: the last product that reads the step's dO tile (dV) is complete
@@ -164,8 +169,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         mbar_init(&sm.bar_do[1], 1);
         mbar_init(&sm.bar_sdp, 1);
         mbar_init(&sm.bar_sfree, 32 * kBwdComputeWarps);
-        mbar_init(&sm.bar_pds, 32 * kBwdComputeWarps);
-        mbar_init(&sm.bar_mma2, 1);
+        mbar_init(&sm.bar_pds[0], 32 * kBwdComputeWarps);
+        mbar_init(&sm.bar_pds[1], 32 * kBwdComputeWarps);
+        mbar_init(&sm.bar_mma2[0], 1);
+        mbar_init(&sm.bar_mma2[1], 1);
         mbar_init(&sm.bar_q_free, 1);
         mbar_init(&sm.bar_do_free, 1);
         mbar_init(&sm.bar_done, 1);
@@ -185,7 +192,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const uint32_t tmem = sm.tmem_base;
 
     const uint32_t a_bar_kv = smem_u32(&sm.bar_kv), a_bar_q = smem_u32(&sm.bar_q[0]), a_bar_do = smem_u32(&sm.bar_do[0]),
-                   a_bar_sdp = smem_u32(&sm.bar_sdp), a_bar_pds = smem_u32(&sm.bar_pds), a_bar_mma2 = smem_u32(&sm.bar_mma2),
+                   a_bar_sdp = smem_u32(&sm.bar_sdp), a_bar_pds = smem_u32(&sm.bar_pds[0]), a_bar_mma2 = smem_u32(&sm.bar_mma2[0]),
                    a_bar_sfree = smem_u32(&sm.bar_sfree), a_bar_q_free = smem_u32(&sm.bar_q_free),
                    a_bar_do_free = smem_u32(&sm.bar_do_free), a_bar_done = smem_u32(&sm.bar_done);
     bool ok = true;  // false once a bounded wait has run out; the same in all lanes of a warp
@@ -261,7 +268,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 // S and dP of the next block go to the tensor core as soon as this block's have left tensor memory,
                 // while the compute warps are still busy with the arithmetic on them
                 if (i_next < nblk) issue_s_dp(g + 1, false);
-                wait(a_bar_pds, g & 1u);
+                wait(a_bar_pds + 8 * (g & 1u), (g >> 1) & 1u);
                 tc_fence_after_sync();
                 const uint32_t q_lo = smem_desc_sw128_lo(smem_u32(sm.q[st])), do_lo = smem_desc_sw128_lo(smem_u32(sm.dout[st]));
                 const uint32_t p_t_lo = p_t_lo0 + st * kStageUnits, ds_t_lo = ds_t_lo0 + st * kStageUnits, ds_k_lo = ds_k_lo0 + st * kStageUnits;
@@ -280,7 +287,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                     for (int kk = 0; kk < kBwdBlock / 16; ++kk)
                         mma_ss_lh(tmem + kBwdColDQ + 64 * st, ds_k_lo + (kk >> 2) * (kBwdPanelBytes >> 4) + 2 * (kk & 3), k_lo + 128 * kk, kHi,
                                   idesc_q, kk ? 1u : 0u);
-                    mma_commit_a(a_bar_mma2);
+                    mma_commit_a(a_bar_mma2 + 8 * st);
                 }
                 __syncwarp();
                 ++s;
@@ -480,7 +487,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             ++half_phase;
         };
         auto read_dq = [&](uint32_t step, float (&dq)[32]) {
-            wait(a_bar_mma2, step & 1u);
+            wait(a_bar_mma2 + 8 * (step & 1u), (step >> 1) & 1u);
             tc_fence_after_sync();
             if (!ok) return;
             tmem_ld32_f32(tmem_lane + kBwdColDQ + 64 * (step & 1u) + 32 * half, dq);
@@ -588,7 +595,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             }
             fence_proxy_async_smem();
             tc_fence_before_sync();
-            mbar_arrive_a(a_bar_pds);
+            mbar_arrive_a(a_bar_pds + 8 * (g & 1u));
             // dQ of the step before (its products ran under this step's arithmetic) leaves tensor memory behind the
             // arrival, which nothing then holds up: the products of this step write the other dQ buffer, and the ones
             // after them, issued behind this thread's next arrival, this one
