@@ -23,6 +23,9 @@
 //                       The walk is software-pipelined: P/dS, Q/dO and dQ exist twice, S and dP of block s+1 are
 //                       issued as soon as the compute warps have read those of block s out of tensor memory, and the
 //                       three products that consume P and dS of block s run under the arithmetic of block s+1.
+//                       Ten warps: eight compute warps, one that issues the products, one that requests the tiles
+//                       (TMA), takes the CTA's next unit from the queue and reads that unit's strip of the mask while
+//                       the unit in work runs, so that the next unit's tiles are on their way before the boundary.
 //   bwd_finish_kernel   dq = round(accumulator)
 //
 // P and dS are the A operands of products that contract over the query rows (P^T, dS^T: "MN-major" operands, read
