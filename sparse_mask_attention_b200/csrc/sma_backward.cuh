@@ -406,7 +406,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             }
             __syncwarp();
             if (i < nblk) {
-                load_q(g & 1u, i);
+#ifdef SMA_WAIT_TEST_BUILD
+                // test build only: on request, the first Q tile of unit 0 is never asked for, nothing completes its
+                // barrier, and the issuing warp's wait for it runs out
+                const bool withheld = g_test_withhold_q_load != 0 && u == 0;
+#else
+                constexpr bool withheld = false;
+#endif
+                if (!withheld) load_q(g & 1u, i);
                 load_do(g & 1u, i);
             }
         };

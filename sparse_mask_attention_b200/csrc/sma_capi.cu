@@ -733,7 +733,8 @@ int sma_attention_fwd_static_workspace(const sma_attention_params* p, void* stre
 }
 
 #ifdef SMA_WAIT_TEST_BUILD
-// Test build only (not declared in include/sma.h): while on, every attention launch leaves one Q tile unrequested.
+// Test build only (not declared in include/sma.h): while on, every attention launch, forward or backward, leaves one
+// Q tile unrequested.
 int sma_test_withhold_q_load(int on) {
     const int value = on ? 1 : 0;
     return cuda_ok(cudaMemcpyToSymbol(sma::g_test_withhold_q_load, &value, sizeof(int))) ? SMA_OK : SMA_ERR_CUDA;
