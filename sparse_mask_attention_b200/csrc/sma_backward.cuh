@@ -81,7 +81,7 @@ struct BwdSmem {
     uint64_t bar_done;      // tensor core: every product of the unit is complete (one phase per unit)
     uint32_t tmem_base;
     uint32_t abort_flag;
-    // Double-buffered by the parity of the CTA's unit count: while a unit is in work the control warp names the one
+    // Double-buffered by the parity of the CTA's unit count: while a unit is in work the loading warp names the one
     // after it and marks that unit's query blocks.
     uint32_t unit_id[2];                          // the unit (>= the number of units: none is left)
     uint32_t qblock_any[2][kBwdMaxQBlocks / 32];  // bit i: query block i keeps something in the keys of the unit
@@ -484,7 +484,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         int prev_row0 = 0;
         // dQ of a finished step leaves through shared memory and one TMA reduction per half (fp32 add into the
         // accumulator in global memory).  Per-thread atomics (8 vector atomics per thread and step) filled the
-        // load/store queue that the control warp's barrier and shared-memory accesses also go through, and held it up
+        // load/store queue that the issuing warp's barrier and shared-memory accesses also go through, and held it up
         // for as long as they took.  The staging tile is the P panel of the finished step, free once its products are
         // complete: [128 rows][32 fp32 = 128 bytes], 128-byte swizzle, this half's columns.
         const bool reducer = (threadIdx.x & 127u) == 0;  // the thread of a half that issues its reductions
@@ -545,7 +545,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             return r;
         };
         for (;;) {
-            // The unit before is over for every thread; the control warp has named this one and marked the query blocks
+            // The unit before is over for every thread; the loading warp has named this one and marked the query blocks
             // that keep anything in its keys.
             __syncthreads();
             const uint32_t slot = unit_no & 1u;
