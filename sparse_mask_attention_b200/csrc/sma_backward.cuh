@@ -111,6 +111,7 @@ __global__ void __launch_bounds__(256)
 bwd_prepare_kernel(const uint32_t* __restrict__ dout, const uint32_t* __restrict__ out, float* __restrict__ delta,
                    float* __restrict__ dq_accum, size_t rows, uint32_t* __restrict__ unit_counter) {
     const int lane = threadIdx.x & 31;
+    grid_launch_dependents();  // attn_bwd_kernel's CTAs may set themselves up as this grid's retire
     if (unit_counter != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *unit_counter = 0u;  // attn_bwd_kernel's work queue
     const size_t warps = static_cast<size_t>(gridDim.x) * (blockDim.x >> 5);
     for (size_t row = static_cast<size_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows; row += warps) {
@@ -136,6 +137,7 @@ bwd_prepare_kernel(const uint32_t* __restrict__ dout, const uint32_t* __restrict
 template <bool kBf16>
 __global__ void __launch_bounds__(256)
 bwd_finish_kernel(const float2* __restrict__ dq_accum, uint32_t* __restrict__ dq, size_t n2) {
+    grid_dependency_wait();  // launched to overlap with attn_bwd_kernel's last CTAs: its reductions are complete from here on
     const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
     for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n2; i += stride) {
         const float2 x = dq_accum[i];
@@ -193,6 +195,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = sm.tmem_base;
+    // Launched to overlap with bwd_prepare_kernel: barriers and tensor memory are set up while that grid drains; its
+    // outputs (delta, the zeroed accumulator, the queue word) are there from here on.  bwd_finish_kernel in turn may
+    // be scheduled as this grid's CTAs retire.
+    grid_dependency_wait();
+    grid_launch_dependents();
 
     const uint32_t a_bar_kv = smem_u32(&sm.bar_kv), a_bar_q = smem_u32(&sm.bar_q[0]), a_bar_do = smem_u32(&sm.bar_do[0]),
                    a_bar_sdp = smem_u32(&sm.bar_sdp), a_bar_pds = smem_u32(&sm.bar_pds[0]), a_bar_mma2 = smem_u32(&sm.bar_mma2[0]),
@@ -332,7 +339,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             __syncwarp();
         };
         // Which query blocks keep anything in the 128 keys of a unit: this warp reads the unit's column strip of
-        // the mask (plain loads: this kernel is launched the ordinary way, everything written before it is visible),
+        // the mask (plain loads: written by kernels that completed before bwd_prepare_kernel started),
         // four query blocks at a time, one lane per four rows of a block.  It does so for the unit AFTER the one in
         // work, between its loads, so that at a unit's end the next unit's tiles can be requested at once.
         const bool scan_vec = (nw & 3) == 0 && (reinterpret_cast<uintptr_t>(args.mask_packed) & 15u) == 0;

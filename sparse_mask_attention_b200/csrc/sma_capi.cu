@@ -371,13 +371,13 @@ static int launch_backward(DeviceInfo* dev, const CUtensorMap& tq, const CUtenso
     // persistent CTAs, one per SM, that share out the (key block, batch*head) units through a queue
     const long long units = static_cast<long long>(args.BH) * ((args.N + sma::kBwdBlock - 1) / sma::kBwdBlock);
     const unsigned blocks = static_cast<unsigned>(units < dev->sm_count ? units : dev->sm_count);
-    if (!cuda_ok(launch_plain(kernel, blocks, sma::kBwdThreads, smem, stream, tq, tk, tv, tdo, tdq, args))) return SMA_ERR_CUDA;
+    if (!cuda_ok(launch_overlapped(kernel, blocks, sma::kBwdThreads, smem, stream, tq, tk, tv, tdo, tdq, args))) return SMA_ERR_CUDA;
     {
         const size_t n2 = rows * sma::kBwdDim / 2;
         size_t blocks2 = (n2 + 255) / 256;
         const size_t cap = static_cast<size_t>(dev->sm_count) * 16;
         if (blocks2 > cap) blocks2 = cap;
-        if (!cuda_ok(launch_plain(sma::bwd_finish_kernel<kBf16>, static_cast<unsigned>(blocks2), 256, 0, stream,
+        if (!cuda_ok(launch_overlapped(sma::bwd_finish_kernel<kBf16>, static_cast<unsigned>(blocks2), 256, 0, stream,
                                   reinterpret_cast<const float2*>(args.dq_accum), static_cast<uint32_t*>(dq), n2)))
             return SMA_ERR_CUDA;
     }
