@@ -560,100 +560,100 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             if (u >= units || *abort_flag) break;
             begin_unit(u);
             uint32_t steps = 0;  // steps of this unit
-        int i = next_block(slot, 0);
-        RowIn in_next = load_row(i);
-        while (i < nblk && ok) {
-            const RowIn in = in_next;
-            const int i_next = next_block(slot, i + 1);
-            in_next = load_row(i_next);
-            uint32_t mw[2] = {in.mw0, in.mw1};
-            float neg_lse_l2 = 0.f;
-            const float delta = in.delta;
-            if (in.lse != -INFINITY) {
-                neg_lse_l2 = -in.lse * 1.4426950408889634f;
-            } else {  // a row that keeps nothing has P = 0 everywhere
-                mw[0] = mw[1] = 0u;
+            int i = next_block(slot, 0);
+            RowIn in_next = load_row(i);
+            while (i < nblk && ok) {
+                const RowIn in = in_next;
+                const int i_next = next_block(slot, i + 1);
+                in_next = load_row(i_next);
+                uint32_t mw[2] = {in.mw0, in.mw1};
+                float neg_lse_l2 = 0.f;
+                const float delta = in.delta;
+                if (in.lse != -INFINITY) {
+                    neg_lse_l2 = -in.lse * 1.4426950408889634f;
+                } else {  // a row that keeps nothing has P = 0 everywhere
+                    mw[0] = mw[1] = 0u;
+                }
+                wait(a_bar_sdp, g & 1u);
+                tc_fence_after_sync();
+                if (!ok) break;
+                // this step's P/dS buffer was last read by the products of the step before last: complete, because this
+                // thread waited for them before it arrived for the step before (below)
+                const uint32_t a_p = a_p0 + (g & 1u) * 2 * kBwdPanelBytes, a_ds = a_ds0 + (g & 1u) * 2 * kBwdPanelBytes;
+                if (g >= 2) staging_free();  // the dQ of the step before last (of this unit or the one before) went out through this P panel
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {  // 32 keys at a time
+                    float s[32], dp[32];
+                    tmem_ld32_f32(tmem_lane + kBwdColS + 64 * half + 32 * c, s);
+                    tmem_ld32_f32(tmem_lane + kBwdColDP + 64 * half + 32 * c, dp);
+                    tmem_wait_ld();
+                    if (c == 1) {  // this thread's part of S and dP is in registers: the tensor core may overwrite it
+                        tc_fence_before_sync();
+                        mbar_arrive_a(a_bar_sfree);
+                    }
+                    const uint32_t bits = mw[c];
+                    uint32_t pw[16], dw[16];
+#pragma unroll
+                    for (int e = 0; e < 32; e += 2) {
+                        const float p0 = ((bits >> e) & 1u) ? ex2_approx(fmaf(s[e], scale_log2e, neg_lse_l2)) : 0.f;
+                        const float p1 = ((bits >> (e + 1)) & 1u) ? ex2_approx(fmaf(s[e + 1], scale_log2e, neg_lse_l2)) : 0.f;
+                        const float d0 = p0 * (dp[e] - delta) * args.scale, d1 = p1 * (dp[e + 1] - delta) * args.scale;
+                        pw[e >> 1] = kBf16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
+                        dw[e >> 1] = kBf16 ? pack_bf16x2(d0, d1) : pack_f16x2(d0, d1);
+                    }
+                    // 32 keys = four 16-byte pieces of this thread's 128-byte row in its panel, pieces 4 c .. 4 c + 3, each
+                    // stored where the 128-byte swizzle puts it
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        const uint32_t piece = ((static_cast<uint32_t>(4 * c + g)) ^ sw) * 16u;
+                        sts_v4(a_p + piece, make_uint4(pw[4 * g], pw[4 * g + 1], pw[4 * g + 2], pw[4 * g + 3]));
+                        sts_v4(a_ds + piece, make_uint4(dw[4 * g], dw[4 * g + 1], dw[4 * g + 2], dw[4 * g + 3]));
+                    }
+                }
+                fence_proxy_async_smem();
+                tc_fence_before_sync();
+                mbar_arrive_a(a_bar_pds + 8 * (g & 1u));
+                // dQ of the step before (its products ran under this step's arithmetic) leaves tensor memory behind the
+                // arrival, which nothing then holds up: the products of this step write the other dQ buffer, and the ones
+                // after them, issued behind this thread's next arrival, this one
+                if (steps >= 1) {
+                    float dq[32];
+                    read_dq(g - 1, dq);
+                    if (ok) reduce_dq(g - 1, dq, prev_row0);
+                }
+                prev_row0 = i * kBwdBlock;
+                ++steps;
+                ++g;
+                i = i_next;
             }
-            wait(a_bar_sdp, g & 1u);
-            tc_fence_after_sync();
-            if (!ok) break;
-            // this step's P/dS buffer was last read by the products of the step before last: complete, because this
-            // thread waited for them before it arrived for the step before (below)
-            const uint32_t a_p = a_p0 + (g & 1u) * 2 * kBwdPanelBytes, a_ds = a_ds0 + (g & 1u) * 2 * kBwdPanelBytes;
-            if (g >= 2) staging_free();  // the dQ of the step before last (of this unit or the one before) went out through this P panel
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {  // 32 keys at a time
-                float s[32], dp[32];
-                tmem_ld32_f32(tmem_lane + kBwdColS + 64 * half + 32 * c, s);
-                tmem_ld32_f32(tmem_lane + kBwdColDP + 64 * half + 32 * c, dp);
-                tmem_wait_ld();
-                if (c == 1) {  // this thread's part of S and dP is in registers: the tensor core may overwrite it
-                    tc_fence_before_sync();
-                    mbar_arrive_a(a_bar_sfree);
-                }
-                const uint32_t bits = mw[c];
-                uint32_t pw[16], dw[16];
-#pragma unroll
-                for (int e = 0; e < 32; e += 2) {
-                    const float p0 = ((bits >> e) & 1u) ? ex2_approx(fmaf(s[e], scale_log2e, neg_lse_l2)) : 0.f;
-                    const float p1 = ((bits >> (e + 1)) & 1u) ? ex2_approx(fmaf(s[e + 1], scale_log2e, neg_lse_l2)) : 0.f;
-                    const float d0 = p0 * (dp[e] - delta) * args.scale, d1 = p1 * (dp[e + 1] - delta) * args.scale;
-                    pw[e >> 1] = kBf16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
-                    dw[e >> 1] = kBf16 ? pack_bf16x2(d0, d1) : pack_f16x2(d0, d1);
-                }
-                // 32 keys = four 16-byte pieces of this thread's 128-byte row in its panel, pieces 4 c .. 4 c + 3, each
-                // stored where the 128-byte swizzle puts it
-#pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    const uint32_t piece = ((static_cast<uint32_t>(4 * c + g)) ^ sw) * 16u;
-                    sts_v4(a_p + piece, make_uint4(pw[4 * g], pw[4 * g + 1], pw[4 * g + 2], pw[4 * g + 3]));
-                    sts_v4(a_ds + piece, make_uint4(dw[4 * g], dw[4 * g + 1], dw[4 * g + 2], dw[4 * g + 3]));
-                }
-            }
-            fence_proxy_async_smem();
-            tc_fence_before_sync();
-            mbar_arrive_a(a_bar_pds + 8 * (g & 1u));
-            // dQ of the step before (its products ran under this step's arithmetic) leaves tensor memory behind the
-            // arrival, which nothing then holds up: the products of this step write the other dQ buffer, and the ones
-            // after them, issued behind this thread's next arrival, this one
-            if (steps >= 1) {
+            if (steps >= 1 && ok) {
                 float dq[32];
                 read_dq(g - 1, dq);
                 if (ok) reduce_dq(g - 1, dq, prev_row0);
             }
-            prev_row0 = i * kBwdBlock;
-            ++steps;
-            ++g;
-            i = i_next;
-        }
-        if (steps >= 1 && ok) {
-            float dq[32];
-            read_dq(g - 1, dq);
-            if (ok) reduce_dq(g - 1, dq, prev_row0);
-        }
-        // ---- dK_j (warps 0-3) and dV_j (warps 4-7): tensor-memory lane t is key 128 j + t ----
-        const int key = j * kBwdBlock + t;
-        if (ok) {
-            uint32_t outw[kBwdDim / 2];
-            if (steps >= 1) {
-                float acc[kBwdDim];
-                const uint32_t col = half ? kBwdColDV : kBwdColDK;
-                tmem_ld32_f32(tmem_lane + col, &acc[0]);
-                tmem_ld32_f32(tmem_lane + col + 32, &acc[32]);
-                tmem_wait_ld();
+            // ---- dK_j (warps 0-3) and dV_j (warps 4-7): tensor-memory lane t is key 128 j + t ----
+            const int key = j * kBwdBlock + t;
+            if (ok) {
+                uint32_t outw[kBwdDim / 2];
+                if (steps >= 1) {
+                    float acc[kBwdDim];
+                    const uint32_t col = half ? kBwdColDV : kBwdColDK;
+                    tmem_ld32_f32(tmem_lane + col, &acc[0]);
+                    tmem_ld32_f32(tmem_lane + col + 32, &acc[32]);
+                    tmem_wait_ld();
 #pragma unroll
-                for (int e = 0; e < kBwdDim; e += 2) outw[e >> 1] = kBf16 ? pack_bf16x2(acc[e], acc[e + 1]) : pack_f16x2(acc[e], acc[e + 1]);
-            } else {
+                    for (int e = 0; e < kBwdDim; e += 2) outw[e >> 1] = kBf16 ? pack_bf16x2(acc[e], acc[e + 1]) : pack_f16x2(acc[e], acc[e + 1]);
+                } else {
 #pragma unroll
-                for (int e = 0; e < kBwdDim / 2; ++e) outw[e] = 0u;  // no query row keeps any of these keys
+                    for (int e = 0; e < kBwdDim / 2; ++e) outw[e] = 0u;  // no query row keeps any of these keys
+                }
+                if (key < N) {
+                    uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(half ? args.dv : args.dk) +
+                                                          (static_cast<size_t>(bh) * N + key) * kBwdDim * 2);
+#pragma unroll
+                    for (int c = 0; c < kBwdDim / 8; ++c) dst[c] = make_uint4(outw[4 * c], outw[4 * c + 1], outw[4 * c + 2], outw[4 * c + 3]);
+                }
             }
-            if (key < N) {
-                uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(half ? args.dv : args.dk) +
-                                                      (static_cast<size_t>(bh) * N + key) * kBwdDim * 2);
-#pragma unroll
-                for (int c = 0; c < kBwdDim / 8; ++c) dst[c] = make_uint4(outw[4 * c], outw[4 * c + 1], outw[4 * c + 2], outw[4 * c + 3]);
-            }
-        }
             // (the next unit's products that overwrite dK and dV in tensor memory are issued behind the CTA-wide barrier
             // above, which this thread reaches after the loads have completed)
             tc_fence_before_sync();
